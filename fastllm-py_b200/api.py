@@ -62,7 +62,8 @@ class Model:
         from .native import build as native_build
         from .native.libraries import libraries_for
         head_dims = [p.head_dim for p in decoder.all_parts() if hasattr(p, "head_dim")]
-        native_build.compile_many(libraries_for(engine_config.dtype, head_dims))
+        named = [lib for p in decoder.all_parts() for lib in getattr(p, "native_libraries", ())]
+        native_build.compile_many(libraries_for(engine_config.dtype, head_dims, named))
         expected = decoder.expected_tensors()
         if isinstance(store, _RandomSpec):
             store = RandomStore(expected, store.seed, store.std, store.norm_std,

@@ -55,6 +55,17 @@ class PagedKV(PagedNeed):
 
 
 @dataclass(frozen=True)
+class PagedRows(PagedNeed):
+    """One vector of `width` elements per token (a compressed key/value latent with a shared
+    rotated key part behind it, say): a page is [page_size, width], rows in token order."""
+    width: int
+    window: int | None = None
+
+    def page_shape(self, page_size: int) -> tuple:
+        return (page_size, self.width)
+
+
+@dataclass(frozen=True)
 class FixedState:
     """State of fixed size per request: a tensor of `shape` in `dtype`
     ("float32", or "activation" for the engine's activation dtype), one row per

@@ -2,8 +2,8 @@
 
 fastllm-py has no registry: one generic forward serves every family and finds
 features by looking at which tensor names exist (fastllm_py/model.py:1-5).
-Here `config.json["architectures"][0]` (or `model_type`, for folders that lack
-it) picks an entry, and an entry is two things: the typed configuration class
+Here `config.json["architectures"][0]` (or the string `architecture`, or
+`model_type`, for folders that lack it) picks an entry, and an entry is two things: the typed configuration class
 and the function that turns a configuration into a ModelPlan, the description
 of the model in terms of parts.  Adding an architecture is one call of
 `register_architecture`; nothing else in the package names an architecture.
@@ -47,6 +47,8 @@ def architecture_of(raw: dict) -> Architecture:
     name = None
     if isinstance(names, list) and names:
         name = names[0]
+    elif isinstance(raw.get("architecture"), str):        # config files that name one architecture, as a string
+        name = raw["architecture"]
     elif isinstance(raw.get("model_type"), str):
         name = _MODEL_TYPES.get(raw["model_type"])
         if name is None:
@@ -54,7 +56,7 @@ def architecture_of(raw: dict) -> Architecture:
                 f"config.json has no 'architectures' and model_type {raw['model_type']!r} "
                 f"is not registered (known: {sorted(_MODEL_TYPES)})")
     if name is None:
-        raise ConfigError("config.json has neither 'architectures' nor 'model_type'")
+        raise ConfigError("config.json has neither 'architectures', 'architecture' nor 'model_type'")
     if name not in _ARCHITECTURES:
         raise ConfigError(
             f"architecture {name!r} is not registered (known: {architecture_names()})")

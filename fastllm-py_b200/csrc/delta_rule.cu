@@ -1,0 +1,253 @@
+// Gated delta rule: a linear-attention mixer whose memory is one matrix per head.
+//
+// Per head, with a state S [dim x vdim] in float that a request carries from token to token:
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// where q, k (unit vectors per head, q times `q_scale`) and v come from projections that pass a short
+// causal convolution over time and silu; beta = sigmoid(b) and g = exp(-exp(A_log) softplus(a + dt_bias))
+// are per head and token.  The read-out sees the token's own write.
+//
+// Four kernels, all float inside:
+//   delta_prep        per token: convolution over the last `taps` inputs (from the step's rows or, before
+//                     the portion's start, from the request's saved tail), silu, unit norms, beta, decay
+//   delta_tail        per request: the last taps - 1 raw inputs of the portion become the saved tail
+//   delta_scan        per (request, head, 32 value columns): the recurrence over the portion's tokens,
+//                     one value column's state spread over eight lanes' registers
+//   delta_gated_norm  per (token, head): o / rms(o) * w * silu(gate)
+//
+// A request's state row is [heads][vdim][dim] floats (a column of S is contiguous) followed by the
+// convolution tail [taps - 1][channels]; channels are q | k | v in the projection's column order.  A
+// portion that starts at position 0 ignores what the row holds.  Every sum's order depends only on the
+// token's place in its sequence, so results do not change with how a sequence is cut or batched.
+#include "common.cuh"
+
+#define DELTA_PARTS 8            // lanes that share one value column
+#define DELTA_COLS 32            // value columns of a block
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256) delta_prep_kernel(
+    const T* __restrict__ proj, long ld, const TW* __restrict__ conv_w, const TW* __restrict__ a_log,
+    const TW* __restrict__ dt_bias, const float* __restrict__ state, long state_stride, long tail_off,
+    const int* __restrict__ tok_req, const int* __restrict__ positions, const int* __restrict__ req_ctx,
+    const int* __restrict__ req_slot, float* __restrict__ work, long work_ld,
+    int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float conv_out[];                      // [channels]
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int qk_cols = kv_heads * dim, hv = heads * vdim;
+    const int channels = 2 * qk_cols + hv;
+    const int r = tok_req[t], pos = positions[t], ctx = req_ctx[r];
+    const float* tail = state + (long)req_slot[r] * state_stride + tail_off;
+    const T* row = proj + (long)t * ld;
+    for (int c = tid; c < channels; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int back = taps - 1; back >= 0; --back) {        // oldest input first
+            const int p = pos - back;
+            if (p < 0) continue;
+            const float x = p >= ctx ? to_f32<T>(row[c - (long)back * ld])
+                                     : tail[(long)(p - ctx + taps - 1) * channels + c];
+            acc += to_f32<TW>(conv_w[(long)c * taps + (taps - 1 - back)]) * x;
+        }
+        conv_out[c] = acc / (1.0f + expf(-acc));
+    }
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31, n_warps = blockDim.x >> 5;
+    float* qk_row = work + (long)t * work_ld;              // work row: q | k | v | beta | decay | o
+    float* v_row = qk_row + 2 * qk_cols;
+    float* bg_row = v_row + hv;
+    for (int hh = warp; hh < 2 * kv_heads; hh += n_warps) {  // query heads, then key heads
+        const float* x = conv_out + hh * dim;
+        float ss = 0.0f;
+        for (int d = lane; d < dim; d += 32) ss += x[d] * x[d];
+        ss = warp_sum(ss);
+        const float f = (hh < kv_heads ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
+        for (int d = lane; d < dim; d += 32) qk_row[hh * dim + d] = x[d] * f;
+    }
+    for (int j = tid; j < hv; j += blockDim.x) v_row[j] = conv_out[2 * qk_cols + j];
+    for (int h = tid; h < heads; h += blockDim.x) {
+        const float b = to_f32<T>(row[channels + hv + h]);
+        const float a = to_f32<T>(row[channels + hv + heads + h]) + to_f32<TW>(dt_bias[h]);
+        const float softplus = a > 20.0f ? a : log1pf(expf(a));
+        bg_row[h] = 1.0f / (1.0f + expf(-b));
+        bg_row[heads + h] = expf(-expf(to_f32<TW>(a_log[h])) * softplus);
+    }
+}
+
+template <typename T>
+__global__ void delta_tail_kernel(const T* __restrict__ proj, long ld, float* __restrict__ state, long state_stride,
+                                  long tail_off, const int* __restrict__ req_start, const int* __restrict__ req_ctx,
+                                  const int* __restrict__ req_qlen, const int* __restrict__ req_slot, int channels,
+                                  int taps) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int start = req_start[r], ctx = req_ctx[r], qlen = req_qlen[r];
+    float* tail = state + (long)req_slot[r] * state_stride + tail_off;
+    // entry j holds the input at position end - (taps - 1) + j; an older entry moves down from j + qlen,
+    // which lies above j, so going upwards in place is safe
+    for (int j = 0; j < taps - 1; ++j) {
+        const int p = ctx + qlen - (taps - 1) + j;
+        float x = 0.0f;
+        if (p >= ctx) x = to_f32<T>(proj[(long)(start + p - ctx) * ld + c]);
+        else if (p >= 0) x = tail[(long)(j + qlen) * channels + c];
+        tail[(long)j * channels + c] = x;
+    }
+}
+
+// One block: one request, one head, DELTA_COLS value columns.  Thread (col, part) keeps the elements
+// d = i * DELTA_PARTS + part of column `col` of S.
+template <int DPT>
+__global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
+    float* __restrict__ work, long work_ld, float* __restrict__ state, long state_stride,
+    const int* __restrict__ req_start, const int* __restrict__ req_ctx, const int* __restrict__ req_qlen,
+    const int* __restrict__ req_slot, int heads, int kv_heads, int dim, int vdim) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x / heads, h = blockIdx.x % heads;
+    const int g = h / (heads / kv_heads);
+    const int part = threadIdx.x & (DELTA_PARTS - 1), col = threadIdx.x / DELTA_PARTS;
+    const int j = blockIdx.y * DELTA_COLS + col;
+    const bool live = j < vdim;
+    const int jj = live ? j : vdim - 1;                      // idle columns shadow the last one and store nothing
+    const int start = req_start[r], qlen = req_qlen[r];
+    float* s_col = state + (long)req_slot[r] * state_stride + ((long)h * vdim + jj) * dim;
+    const int qk_cols = kv_heads * dim, hv = heads * vdim;
+    float S[DPT], k[DPT], q[DPT], k_next[DPT], q_next[DPT];
+    const bool fresh = req_ctx[r] == 0;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = i * DELTA_PARTS + part;
+        S[i] = (!fresh && d < dim) ? s_col[d] : 0.0f;
+        k_next[i] = q_next[i] = 0.0f;
+    }
+    // the next token's inputs are asked for before this token's arithmetic: they do not depend on S
+    auto fetch = [&](int t, float* kk, float* qq, float& v, float& beta, float& decay) {
+        const float* row = work + (long)t * work_ld;
+        const float* qrow = row + g * dim;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = i * DELTA_PARTS + part;
+            kk[i] = d < dim ? qrow[qk_cols + d] : 0.0f;
+            qq[i] = d < dim ? qrow[d] : 0.0f;
+        }
+        v = row[2 * qk_cols + h * vdim + jj];
+        beta = row[2 * qk_cols + hv + h];
+        decay = row[2 * qk_cols + hv + heads + h];
+    };
+    float v, beta, decay, v_next = 0.0f, beta_next = 0.0f, decay_next = 0.0f;
+    fetch(start, k, q, v, beta, decay);
+    for (int n = 0; n < qlen; ++n) {
+        if (n + 1 < qlen) fetch(start + n + 1, k_next, q_next, v_next, beta_next, decay_next);
+        float dot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) dot += S[i] * k[i];
+#pragma unroll
+        for (int o = 1; o < DELTA_PARTS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float u = beta * (v - decay * dot);
+        float out = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            S[i] = decay * S[i] + k[i] * u;
+            out += S[i] * q[i];
+        }
+#pragma unroll
+        for (int o = 1; o < DELTA_PARTS; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+        if (live && part == 0) work[(long)(start + n) * work_ld + 2 * qk_cols + hv + 2 * heads + h * vdim + j] = out;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) { k[i] = k_next[i]; q[i] = q_next[i]; }
+        v = v_next; beta = beta_next; decay = decay_next;
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = i * DELTA_PARTS + part;
+            if (d < dim) s_col[d] = S[i];
+        }
+    }
+}
+
+// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * silu(gate[t, h, :]); one warp per (token, head).
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) delta_gated_norm_kernel(const float* __restrict__ o, long o_ld, const T* __restrict__ gate,
+                                                               long gate_ld, const TW* __restrict__ w, T* __restrict__ out,
+                                                               long out_ld, int heads, int vdim, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * 4 + (threadIdx.x >> 5);
+    if (h >= heads) return;
+    const float* x = o + (long)t * o_ld + h * vdim;
+    const T* gr = gate + (long)t * gate_ld + h * vdim;
+    T* dst = out + (long)t * out_ld + h * vdim;
+    float ss = 0.0f;
+    for (int i = lane; i < vdim; i += 32) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int i = lane; i < vdim; i += 32) {
+        const float z = to_f32<T>(gr[i]);
+        dst[i] = from_f32<T>(x[i] * inv * to_f32<TW>(w[i]) * (z / (1.0f + expf(-z))));
+    }
+}
+
+// proj: [n_tokens, ld] with columns q | k | v | gate | b | a.
+FL_API int fl_delta_prep(const void* proj, int dtype, long ld, const void* conv_w, const void* a_log, const void* dt_bias,
+                         int w_dtype, float* state, long state_stride, long tail_off, const int* tok_req,
+                         const int* positions, const int* req_start, const int* req_ctx, const int* req_qlen,
+                         const int* req_slot, float* work, long work_ld, int n_tokens, int n_requests,
+                         int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale,
+                         cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int channels = 2 * kv_heads * dim + heads * vdim;
+    if (taps < 1 || heads % kv_heads || n_requests > 65535 || (size_t)channels * sizeof(float) > 48 * 1024)
+        return (int)cudaErrorInvalidValue;
+    int rc = 0;
+    FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
+        rc = fl_launch(delta_prep_kernel<T, TW>, dim3(n_tokens), dim3(256), (size_t)channels * sizeof(float), stream,
+                       (const T*)proj, ld, (const TW*)conv_w, (const TW*)a_log, (const TW*)dt_bias, (const float*)state,
+                       state_stride, tail_off, tok_req, positions, req_ctx, req_slot, work, work_ld, heads, kv_heads,
+                       dim, vdim, taps, unit_eps, q_scale)));
+    if (rc || taps == 1) return rc;
+    FL_DISPATCH(dtype, T,
+        return fl_launch(delta_tail_kernel<T>, dim3((channels + 255) / 256, n_requests), dim3(256), 0, stream,
+                         (const T*)proj, ld, state, state_stride, tail_off, req_start, req_ctx, req_qlen, req_slot,
+                         channels, taps));
+    return 0;
+}
+
+// work: [n_tokens, work_ld] floats, a row = q | k (kv_heads x dim each) | v (heads x vdim) | beta | decay (heads
+// each) | o (heads x vdim): fl_delta_prep fills all but o, fl_delta_scan reads them and fills o.
+FL_API int fl_delta_scan(float* work, long work_ld, float* state, long state_stride,
+                         const int* req_start, const int* req_ctx, const int* req_qlen, const int* req_slot,
+                         int n_requests, int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (heads % kv_heads || dim < 1 || dim > 32 * DELTA_PARTS) return (int)cudaErrorInvalidValue;
+    const int per_thread = (dim + DELTA_PARTS - 1) / DELTA_PARTS;
+    dim3 grid(n_requests * heads, (vdim + DELTA_COLS - 1) / DELTA_COLS);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+#define FL_DELTA_SCAN(DPT)                                                                                          \
+    if (per_thread <= DPT)                                                                                          \
+        return fl_launch(delta_scan_kernel<DPT>, grid, dim3(DELTA_COLS * DELTA_PARTS), 0, stream, work, work_ld, state, \
+                         state_stride, req_start, req_ctx, req_qlen, req_slot, heads, kv_heads, dim, vdim)
+    FL_DELTA_SCAN(2);
+    FL_DELTA_SCAN(4);
+    FL_DELTA_SCAN(8);
+    FL_DELTA_SCAN(12);
+    FL_DELTA_SCAN(16);
+    FL_DELTA_SCAN(24);
+    FL_DELTA_SCAN(32);
+#undef FL_DELTA_SCAN
+    return (int)cudaErrorInvalidValue;
+}
+
+FL_API int fl_delta_gated_norm(const float* o, long o_ld, const void* gate, int dtype, long gate_ld, const void* w, int w_dtype,
+                               void* out, long out_ld, int n_tokens, int heads, int vdim, float eps, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    dim3 grid(n_tokens, (heads + 3) / 4);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
+        return fl_launch(delta_gated_norm_kernel<T, TW>, grid, dim3(128), 0, stream, o, o_ld, (const T*)gate, gate_ld,
+                         (const TW*)w, (T*)out, out_ld, heads, vdim, eps)));
+    return 0;
+}

@@ -449,3 +449,106 @@ FL_API int fl_swiglu_partial(const float* partial, int splits, long split_stride
                                                 splits, split_stride, ld, (TO*)out, out_ld, inter));
     return 0;
 }
+
+// ------------------------------------------------- gated linear unit, any activation
+// out[r, i] = act(gu[r, i]) * gu[r, inter + i].  act: 0 silu, 1 relu, 2 gelu (tanh form).
+enum FlAct : int { FL_ACT_SILU = 0, FL_ACT_RELU = 1, FL_ACT_GELU_TANH = 2 };
+
+__device__ __forceinline__ float fl_act(float g, int act) {
+    if (act == FL_ACT_RELU) return fmaxf(g, 0.0f);
+    if (act == FL_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-g));
+}
+
+template <typename T>
+__global__ void glu_kernel(const T* __restrict__ gu, long gu_ld, T* __restrict__ out, long out_ld, int inter, int act) {
+    pdl_wait();
+    pdl_trigger();
+    const T* g = gu + (long)blockIdx.y * gu_ld;
+    T* o = out + (long)blockIdx.y * out_ld;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < inter) o[i] = from_f32<T>(fl_act(to_f32<T>(g[i]), act) * to_f32<T>(g[inter + i]));
+}
+
+FL_API int fl_glu(const void* gu, int dtype, long gu_ld, void* out, long out_ld, int n_rows, int inter, int act,
+                  cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows > 65535 || act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+    dim3 grid((inter + 255) / 256, n_rows);
+    FL_DISPATCH(dtype, T, return fl_launch(glu_kernel<T>, grid, dim3(256), 0, stream, (const T*)gu, gu_ld, (T*)out,
+                                           out_ld, inter, act));
+    return 0;
+}
+
+// ------------------------------------------------- norm on both sides of a sublayer
+// A layer that norms a sublayer's output before adding it (x <- x + norm_b(y)) and norms the sum again
+// for the next sublayer, in one pass over the row:
+//     r = y * (mean(y^2) + eps_post)^-1/2 * w_post;  x += r;  out = x * (mean(x^2) + eps_pre)^-1/2 * w_pre
+// x is the float residual stream (written back unless rows are gathered), y the sublayer's output.
+// The summed row waits in shared memory between the second reduction and the last pass.
+template <typename TD, typename TW, typename TO>
+__global__ void sandwich_norm_kernel(float* __restrict__ x, long x_ld, const TD* __restrict__ y, long y_ld,
+                                     const TW* __restrict__ w_post, float eps_post, const TW* __restrict__ w_pre,
+                                     float eps_pre, TO* __restrict__ out, long out_ld, int dim,
+                                     const int* __restrict__ rows, int write_back) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float sandwich_row[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long src = rows ? (long)rows[r] : (long)r;
+    float* xr = x + src * x_ld;
+    const TD* yr = y + src * y_ld;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = to_f32<TD>(yr[i]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv_post = 1.0f / sqrtf(ss / (float)dim + eps_post);
+    ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = xr[i] + to_f32<TD>(yr[i]) * inv_post * to_f32<TW>(w_post[i]);
+        if (write_back) xr[i] = v;
+        sandwich_row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    if (out == nullptr) return;
+    const float inv_pre = 1.0f / sqrtf(ss / (float)dim + eps_pre);
+    TO* o = out + (long)r * out_ld;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        o[i] = from_f32<TO>(sandwich_row[i] * inv_pre * to_f32<TW>(w_pre[i]));
+}
+
+// `out` may be null: only x += norm_post(y) then (w_pre is not read).
+FL_API int fl_sandwich_norm(float* x, long x_ld, const void* y, int y_dtype, long y_ld, const void* w_post,
+                            float eps_post, const void* w_pre, float eps_pre, int w_dtype, void* out, int out_dtype,
+                            long out_ld, int n_rows, int dim, const int* rows, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if ((size_t)dim * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const int write_back = rows ? 0 : 1;
+    int threads = (dim + 31) / 32 * 32;
+    threads = threads > 512 ? 512 : threads;
+    FL_DISPATCH(y_dtype, TD, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
+        return fl_launch(sandwich_norm_kernel<TD, TW, TO>, dim3(n_rows), dim3(threads), (size_t)dim * sizeof(float),
+                         stream, x, x_ld, (const TD*)y, y_ld, (const TW*)w_post, eps_post, (const TW*)w_pre, eps_pre,
+                         (TO*)out, out_ld, dim, rows, write_back))));
+    return 0;
+}
+
+// ------------------------------------------------- soft cap of logits
+// x <- cap * tanh(x / cap), in place, float.
+__global__ void softcap_kernel(float* __restrict__ x, long ld, int cols, float cap) {
+    pdl_wait();
+    pdl_trigger();
+    float* r = x + (long)blockIdx.y * ld;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < cols) r[i] = cap * tanhf(r[i] / cap);
+}
+
+FL_API int fl_softcap(float* x, long ld, int n_rows, int cols, float cap, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows > 65535) return (int)cudaErrorInvalidValue;
+    return fl_launch(softcap_kernel, dim3((cols + 255) / 256, n_rows), dim3(256), 0, stream, x, ld, cols, cap);
+}

@@ -17,9 +17,12 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A, long lda,
                                                         const TW* __restrict__ W, long ldw,
                                                         TC* __restrict__ C, long ldc, int M, int N,
-                                                        int K) {
+                                                        int K, long a_batch, long w_batch, long c_batch) {
     pdl_wait();
     pdl_trigger();
+    A += blockIdx.z * a_batch;                // a batch of products over column blocks of wider buffers
+    W += blockIdx.z * w_batch;
+    C += blockIdx.z * c_batch;
     __shared__ float As[GS_BK][GS_BM + 1];
     __shared__ float Ws[GS_BK][GS_BN + 1];
     const int tid = threadIdx.x;
@@ -69,6 +72,21 @@ FL_API int fl_gemm_simt(const void* A, int a_dtype, long lda, const void* W, int
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     FL_DISPATCH(a_dtype, TA, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(c_dtype, TC,
         return fl_launch(gemm_simt_kernel<TA, TW, TC>, grid, dim3(256), 0, stream, (const TA*)A, lda,
-                         (const TW*)W, ldw, (TC*)C, ldc, M, N, K))));
+                         (const TW*)W, ldw, (TC*)C, ldc, M, N, K, 0L, 0L, 0L))));
+    return 0;
+}
+
+// `batch` products of one shape in one launch: product b reads A + b * a_batch and W + b * w_batch and
+// writes C + b * c_batch (strides in elements).  With a_batch and c_batch smaller than a row this is a
+// product per head over the column blocks of [M, heads x K] and [M, heads x N] buffers.
+FL_API int fl_gemm_simt_batched(const void* A, int a_dtype, long lda, long a_batch, const void* W, int w_dtype,
+                                long ldw, long w_batch, void* C, int c_dtype, long ldc, long c_batch, int M, int N,
+                                int K, int batch, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM, batch);
+    if (grid.y > 65535 || batch > 65535) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(a_dtype, TA, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(c_dtype, TC,
+        return fl_launch(gemm_simt_kernel<TA, TW, TC>, grid, dim3(256), 0, stream, (const TA*)A, lda,
+                         (const TW*)W, ldw, (TC*)C, ldc, M, N, K, a_batch, w_batch, c_batch))));
     return 0;
 }

@@ -221,6 +221,171 @@ def swiglu(gate_up, out):
               out.shape[1], _stream()), "swiglu")
 
 
+def glu(gate_up, out, activation: str = "silu"):
+    """out[:, i] = act(gate_up[:, i]) * gate_up[:, I + i], I = out.shape[1]; act: silu, relu, gelu_tanh."""
+    _require_cuda(gate_up, out)
+    if gate_up.dtype != out.dtype:
+        raise KernelError("glu: input and output must have one dtype")
+    fn = _fn("elementwise", "fl_glu", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(gate_up), dtype_code(gate_up), _ld(gate_up), _ptr(out), _ld(out), out.shape[0],
+              out.shape[1], activation_code(activation), _stream()), "glu")
+
+
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def activation_code(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"activation {name!r} is not one of {sorted(ACTIVATIONS)}") from None
+
+
+def sandwich_norm(resid, y, w_post, eps_post, w_pre, eps_pre, out, rows=None):
+    """resid += rmsnorm(y) * w_post (written back unless rows are gathered); out = rmsnorm(resid) * w_pre.
+    With `out` None only the first half is done."""
+    _require_cuda(resid, y, w_post, w_pre, out, rows)
+    if resid.dtype != torch.float32:
+        raise KernelError("sandwich_norm: the residual stream must be float32")
+    if w_pre is not None and w_pre.dtype != w_post.dtype:
+        raise KernelError("sandwich_norm: both norm weights must be stored in one dtype")
+    fn = _fn("elementwise", "fl_sandwich_norm", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_float, c_void_p,
+                                                 c_float, c_int, c_void_p, c_int, c_long, c_int, c_int, c_void_p,
+                                                 c_void_p])
+    n_rows = resid.shape[0] if rows is None else rows.numel()
+    _check(fn(_ptr(resid), _ld(resid), _ptr(y), dtype_code(y), _ld(y), _ptr(w_post), float(eps_post), _ptr(w_pre),
+              float(eps_pre), dtype_code(w_post), _ptr(out), F32 if out is None else dtype_code(out),
+              0 if out is None else _ld(out), n_rows, resid.shape[1], _ptr(rows), _stream()), "sandwich_norm")
+
+
+def softcap(logits, cap: float):
+    """logits <- cap * tanh(logits / cap), in place (float32)."""
+    _require_cuda(logits)
+    if logits.dtype != torch.float32:
+        raise KernelError("softcap: logits must be float32")
+    fn = _fn("elementwise", "fl_softcap", [c_void_p, c_long, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(logits), _ld(logits), logits.shape[0], logits.shape[1], float(cap), _stream()), "softcap")
+
+
+# ---------------------------------------------------------------- delta rule
+
+def delta_prep(proj, conv_w, a_log, dt_bias, state, tail_off, step, work, heads, kv_heads, dim, vdim, taps,
+               unit_eps, q_scale):
+    """Convolution, silu, unit norms, beta and decay of every token of the step (and the requests' new
+    convolution tails); proj columns are q | k | v | gate | b | a, state rows [S | tail] float32, work
+    rows q | k | v | beta | decay | o float32."""
+    _require_cuda(proj, conv_w, a_log, dt_bias, state, work)
+    if state.dtype != torch.float32 or work.dtype != torch.float32:
+        raise KernelError("delta_prep: state and work buffer must be float32")
+    if not (conv_w.dtype == a_log.dtype == dt_bias.dtype):
+        raise KernelError("delta_prep: the mixer's small tensors must be stored in one dtype")
+    fn = _fn("delta_rule", "fl_delta_prep", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                             c_long, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int,
+                                             c_int, c_float, c_float, c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(conv_w), _ptr(a_log), _ptr(dt_bias), dtype_code(conv_w),
+              _ptr(state), state.stride(0), tail_off, _ptr(step.tok_req), _ptr(step.positions), _ptr(step.req_start),
+              _ptr(step.req_ctx), _ptr(step.req_qlen), _ptr(step.req_slot), _ptr(work), _ld(work),
+              proj.shape[0], step.n_requests, heads, kv_heads, dim, vdim, taps, float(unit_eps), float(q_scale),
+              _stream()), "delta_prep", 1 if taps == 1 else 2)
+
+
+def delta_scan(work, state, step, heads, kv_heads, dim, vdim):
+    """The recurrence over each request's tokens of the step; state rows are read (unless the request
+    starts) and written; the o columns of `work` are filled."""
+    _require_cuda(work, state)
+    fn = _fn("delta_rule", "fl_delta_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(work), _ld(work), _ptr(state), state.stride(0), _ptr(step.req_start), _ptr(step.req_ctx),
+              _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, kv_heads, dim, vdim,
+              _stream()), "delta_scan")
+
+
+def delta_gated_norm(work, o_col, proj, gate_col, weight, out, heads, vdim, eps):
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]); o are the float32 columns of `work`
+    from `o_col` on, gate the columns of `proj` from `gate_col` on."""
+    _require_cuda(work, proj, weight, out)
+    if proj.dtype != out.dtype or work.dtype != torch.float32:
+        raise KernelError("delta_gated_norm: gate and out share a dtype, o is float32")
+    fn = _fn("delta_rule", "fl_delta_gated_norm", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p,
+                                                   c_long, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(c_void_p(work.data_ptr() + 4 * o_col), _ld(work), c_void_p(proj.data_ptr() + proj.element_size() * gate_col),
+              dtype_code(proj), _ld(proj), _ptr(weight), dtype_code(weight), _ptr(out), _ld(out),
+              out.shape[0], heads, vdim, float(eps), _stream()), "delta_gated_norm")
+
+
+# ---------------------------------------------------------- latent attention
+
+def latent_prep(proj, q_out, heads, dim, rot, rank, norm_w, eps, cos, sin, positions, slots, cache):
+    """The queries' rotated parts, turned, go to the last `rot` columns of each head's block of `q_out`
+    (float32 [N, heads * (rank + rot)]); with `cache` ([pages, page_size, rank + rot]), each token's latent
+    is normed and written with the rotated key part into the token's row."""
+    _require_cuda(proj, q_out, norm_w, cos, sin, positions, slots, cache)
+    if cache is not None and (cache.dtype != proj.dtype or not cache.is_contiguous()):
+        raise KernelError("latent_prep: the cache must be contiguous and of the activations' dtype")
+    if q_out.dtype != torch.float32:
+        raise KernelError("latent_prep: q_out must be float32")
+    fn = _fn("latent_attention", "fl_latent_prep", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int,
+                                                    c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                                                    c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(q_out), _ld(q_out), proj.shape[0], heads, dim, rot, rank,
+              _ptr(norm_w), F32 if norm_w is None else dtype_code(norm_w), float(eps), _ptr(cos), _ptr(sin),
+              _ptr(positions), _ptr(slots), _ptr(cache), 0 if cache is None else 1, _stream()), "latent_prep")
+
+
+def latent_attention(q, out, cache, block_table, tok_req, positions, heads, rank, rot, window, scale, page_size):
+    """Attention of every token over its request's cache rows; q [N, heads * (rank + rot)] and
+    out [N, heads * rank] float32."""
+    _require_cuda(q, out, cache, block_table, tok_req, positions)
+    if q.dtype != torch.float32 or out.dtype != torch.float32:
+        raise KernelError("latent_attention: q and out must be float32")
+    fn = _fn("latent_attention", "fl_latent_attention", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int,
+                                                         c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                         c_int, c_float, c_void_p])
+    _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), dtype_code(cache), page_size, _ptr(block_table),
+              block_table.stride(0), _ptr(tok_req), _ptr(positions), q.shape[0], heads, rank, rot, int(window or 0),
+              float(scale), _stream()), "latent_attention")
+
+
+def gemm_simt_batched(a, a_batch, w, out, out_batch):
+    """out[:, b * out_batch : b * out_batch + N] = a[:, b * a_batch : b * a_batch + K] @ w[b]^T for every b:
+    w is [batch, N, K]; a and out are 2-D buffers whose column blocks are the batch."""
+    _require_cuda(a, w, out)
+    batch, n, k = w.shape
+    if not w.is_contiguous():
+        raise KernelError("gemm_simt_batched: the weights must be contiguous")
+    fn = _fn("gemm_simt", "fl_gemm_simt_batched", [c_void_p, c_int, c_long, c_long, c_void_p, c_int, c_long, c_long,
+                                                   c_void_p, c_int, c_long, c_long, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(a), dtype_code(a), _ld(a), a_batch, _ptr(w), dtype_code(w), k, n * k, _ptr(out), dtype_code(out),
+              _ld(out), out_batch, a.shape[0], n, k, batch, _stream()), "gemm_simt_batched")
+
+
+# ------------------------------------------------------------- routed experts
+
+def moe_route(h, w_router, bias, chosen, weights, top, softmax_scores=False, renormalise=False):
+    """Per token the `top` experts by score + bias (int32 `chosen` [N, top]) and their scores (`weights`)."""
+    _require_cuda(h, w_router, bias, chosen, weights)
+    if bias is not None and bias.dtype != w_router.dtype:
+        raise KernelError("moe_route: router matrix and bias must be stored in one dtype")
+    fn = _fn("moe", "fl_moe_route", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                     c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(h), dtype_code(h), _ld(h), _ptr(w_router), _ptr(bias), dtype_code(w_router), _ptr(chosen),
+              _ptr(weights), h.shape[0], h.shape[1], w_router.shape[0], top, int(softmax_scores), int(renormalise),
+              _stream()), "moe_route")
+
+
+def moe_experts(h, w_gate_up, w_down, chosen, weights, act_buf, out, activation="silu"):
+    """out[t] = sum_k weights[t, k] * down[e](act(gate[e] h[t]) * (up[e] h[t])), e = chosen[t, k];
+    w_gate_up [E, 2 ff, width], w_down [E, width, ff]; act_buf float32 [N * top, ff]."""
+    _require_cuda(h, w_gate_up, w_down, chosen, weights, act_buf, out)
+    experts, ff2, width = w_gate_up.shape
+    fn = _fn("moe", "fl_moe_experts", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(h), dtype_code(h), _ld(h), _ptr(w_gate_up), _ptr(w_down), dtype_code(w_gate_up), _ptr(chosen),
+              _ptr(weights), _ptr(act_buf), _ptr(out), _ld(out), h.shape[0], width, ff2 // 2, chosen.shape[1],
+              activation_code(activation), _stream()), "moe_experts", 2)
+
+
 # -------------------------------------------------------------- rope + cache
 
 def rope_kv_write(qkv, n_heads, n_kv_heads, head_dim, rot_dim, cos, sin, positions, slots, cache,
@@ -305,5 +470,5 @@ def apply_penalties(logits, rows, tokens, counts, repetition, frequency, presenc
 
 # ---------------------------------------------------------------------- build
 
-BASE_LIBRARIES = ["elementwise", "rope_kv", "attention_simt", "gemm_simt", "sampling"]
+BASE_LIBRARIES = ["elementwise", "gemm_simt", "sampling"]      # every model; a part names what else it needs
 BF16_LIBRARIES = ["gemm_tcgen05"]

@@ -29,6 +29,7 @@ class Attention(Part):
     window (None | int), shares_cache (bool), scale (None -> head_dim^-1/2).
     tensors: q, o and, unless shares_cache, k, v."""
     category = "mixer"
+    native_libraries = ("rope_kv", "attention_simt")       # beside the head-size builds of native/attention.py
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)

@@ -31,6 +31,8 @@ What a part may declare beside its interface (all optional; absent means "no"):
   graph_safe = False       any part whose forward decides on the host from the step's host copies
   takes_partial = True     norm: `apply` accepts split-K partial sums as the stream's pending sum
                            (otherwise the stream adds them up into a tensor first)
+  takes_post_norm = True   norm: `apply` understands `stream.pending_norm` (the pending sum is normed by
+                           that part before it is added); such a norm also has `add_normed(stream)`
   takes_fed_tokens = True  embedding: understands a token id -1 - r as "row r of `step.token_feed`"
                            (without it the scheduler never launches a step ahead of the host)
 """
@@ -97,14 +99,17 @@ class ResidualStream:
     def __init__(self, x: torch.Tensor, spill=None):
         self.x = x
         self.pending = None
-        self.spill = spill
+        self.pending_norm = None     # a norm part the pending sum passes before it is added (blocks that norm
+        self.spill = spill           # a sublayer's output); a norm with `takes_post_norm` does both in one kernel
 
     def norm_into(self, norm, out, rows=None):
         """`norm.apply(self, out, rows)`, with a pending sum that the norm can take."""
         pending = self.pending
         if pending is not None and not isinstance(pending, torch.Tensor):
-            if rows is not None or not getattr(norm, "takes_partial", False):
-                self.pending = pending.reduce_into(self.spill())
+            if rows is not None or self.pending_norm is not None or not getattr(norm, "takes_partial", False):
+                pending = self.pending = pending.reduce_into(self.spill())
+        if pending is not None and self.pending_norm is not None and not getattr(norm, "takes_post_norm", False):
+            self.pending_norm.add_normed(self)           # x += norm(pending), for a norm that cannot do it itself
         norm.apply(self, out, rows)
 
 

@@ -3,6 +3,11 @@
 "prenorm" is the Llama layer (fastllm_py/model.py:464-470):
     x = x + mixer(norm_mixer(x));  x = x + feed_forward(norm_ff(x))
 The sums are left pending on the residual stream and folded into the next norm.
+
+"sandwich" norms each sublayer on both sides:
+    x = x + norm_mixer_out(mixer(norm_mixer_in(x)));  x = x + norm_ff_out(ff(norm_ff_in(x)))
+and may have no feed-forward at all.  The sublayer's output is left pending with
+its norm; the next norm of the stream does norm, add and norm in one kernel.
 """
 from __future__ import annotations
 
@@ -39,3 +44,40 @@ class PreNormBlock(Part):
         stream.norm_into(self.norm_ff, h)
         left = self.feed_forward.forward(h, delta, step)
         stream.pending = delta if left is None else left
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Part):
+    """norm roles: "mixer_in", "mixer_out" and, with a feed-forward, "ff_in", "ff_out"."""
+    category = "block"
+
+    def __init__(self, layer_spec, ctx):
+        super().__init__(layer_spec, ctx)
+        self.mixer = build_part("mixer", layer_spec.mixer, ctx)
+        self.norm_mixer_in = build_part("norm", layer_spec.norms["mixer_in"], ctx)
+        self.norm_mixer_out = build_part("norm", layer_spec.norms["mixer_out"], ctx)
+        self.feed_forward = self.norm_ff_in = self.norm_ff_out = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, ctx)
+            self.norm_ff_in = build_part("norm", layer_spec.norms["ff_in"], ctx)
+            self.norm_ff_out = build_part("norm", layer_spec.norms["ff_out"], ctx)
+        self.hidden = self.norm_mixer_in.size
+
+    def children(self):
+        parts = [self.mixer, self.norm_mixer_in, self.norm_mixer_out]
+        if self.feed_forward is not None:
+            parts += [self.feed_forward, self.norm_ff_in, self.norm_ff_out]
+        return parts
+
+    def forward(self, stream, step, cache):
+        n = stream.x.shape[0]
+        dt = self.ctx.dtype
+        h = step.workspace.rows("normed", n, self.hidden, dt)
+        delta = step.workspace.rows("delta", n, self.hidden, dt)
+        stream.norm_into(self.norm_mixer_in, h)
+        left = self.mixer.forward(h, delta, step, cache)
+        stream.pending, stream.pending_norm = (delta if left is None else left), self.norm_mixer_out
+        if self.feed_forward is not None:
+            stream.norm_into(self.norm_ff_in, h)
+            left = self.feed_forward.forward(h, delta, step)
+            stream.pending, stream.pending_norm = (delta if left is None else left), self.norm_ff_out

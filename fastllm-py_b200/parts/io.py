@@ -1,7 +1,8 @@
 """Embedding and output head.
 
 Embedding: x = table[ids], no scaling (fastllm_py/model.py:447).  Head:
-logits = x @ W^T in float, no bias, no soft cap (model.py:476); with tied
+logits = x @ W^T in float, no bias (model.py:476), then, for a head with a
+`softcap` c, logits <- c * tanh(logits / c); with tied
 embeddings the head's matrix is the embedding table itself (model.py:228-231),
 which the loader expresses by giving both parts the same tensor."""
 from __future__ import annotations
@@ -36,13 +37,14 @@ class Embedding(Part):
 
 @register_part("head", "linear")
 class LinearHead(Part):
-    """params: vocab_size, hidden_size.  tensors: weight [vocab, hidden]."""
+    """params: vocab_size, hidden_size, softcap (None | c > 0).  tensors: weight [vocab, hidden]."""
     category = "head"
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.softcap = spec.params.get("softcap")
         self.linear = None
 
     def weight_shapes(self):
@@ -59,3 +61,5 @@ class LinearHead(Part):
 
     def forward(self, h, out):
         self.linear.forward(h, out)
+        if self.softcap:
+            ops.softcap(out, self.softcap)

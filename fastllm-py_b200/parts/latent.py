@@ -1,0 +1,112 @@
+"""Latent attention mixer: attention over a compressed per-token cache.
+
+Per token the layer caches one latent vector c (`kv_rank` elements: the first
+rows of W_dkv h, RMS-normed with a weight) and one rotated key part (`rot_dim`
+elements: the last rows of W_dkv h after rotary encoding) that all heads share.
+Head h's key is [W_uk,h c | rotated part], its value W_uv,h c, its query
+[q_plain | rotary(q_rot)] from W_q h laid out head by head; the score is their
+dot product times `scale`, over the keys at or before the query and within
+`window` if the layer has one; softmax in float; W_o on the concatenated heads.
+
+Keys and values are never made.  The query's plain part is carried through
+W_uk,h^T into latent space (q~ = [W_uk,h^T q_plain | q_rot], `kv_rank + rot_dim`
+elements), attention runs on the cache rows themselves, and the weighted sum of
+latents goes through W_uv,h: the same sums in another order, and the cache is
+read once for all heads.  The per-head products take W_uk and W_uv re-laid at
+load as [heads, kv_rank, dim] and [heads, vdim, kv_rank].
+
+A layer with `shares_cache` has no W_dkv: it reads the rows another layer's run
+wrote, with its own queries, W_uk, W_uv, window and scale.  The cache keeps what
+the widest window among the layers that read it needs (`keep`).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.needs import PagedRows
+from ..native import ops
+from .base import Part
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Part):
+    """params: hidden_size, heads, dim, rot_dim, vdim, kv_rank, scale, window (None | int), keep (None | int: what the
+    cache keeps; absent: `window`), norm_eps, position (PartSpec of rot_dim dims), shares_cache (bool).
+    tensors: q [heads * (dim + rot_dim), hidden], uk [heads * dim, kv_rank], uv [heads * vdim, kv_rank],
+    o [hidden, heads * vdim] and, unless shares_cache, dkv [kv_rank + rot_dim, hidden], dkv_norm [kv_rank]."""
+    category = "mixer"
+    native_libraries = ("latent_attention",)
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.dim, self.rot = int(p["heads"]), int(p["dim"]), int(p["rot_dim"])
+        self.vdim, self.rank = int(p["vdim"]), int(p["kv_rank"])
+        self.scale = float(p["scale"])
+        self.window = p.get("window")
+        self.keep = p["keep"] if "keep" in p else self.window
+        self.norm_eps = float(p["norm_eps"])
+        self.shares_cache = bool(p.get("shares_cache", False))
+        if self.rank > 1024:
+            raise ValueError(f"latent_attention: kv_rank {self.rank} is beyond the kernel's limit of 1024")
+        if self.window is not None and self.keep is not None and self.keep < self.window:
+            raise ValueError("latent_attention: the cache keeps fewer tokens than the window sees")
+        self.position = build_part("position", p["position"], ctx)
+        if self.position.rot_dim != self.rot:
+            raise ValueError("latent_attention: the position encoding must turn exactly rot_dim dimensions")
+        self.q_cols = self.heads * (self.dim + self.rot)
+        self.width = self.rank + self.rot                               # a cache row
+        self.proj = self.o = None
+
+    def children(self):
+        return [self.position]
+
+    def cache_need(self):
+        return None if self.shares_cache else PagedRows(self.width, self.keep)
+
+    def weight_shapes(self):
+        shapes = {"q": (self.q_cols, self.hidden), "uk": (self.heads * self.dim, self.rank),
+                  "uv": (self.heads * self.vdim, self.rank), "o": (self.hidden, self.heads * self.vdim)}
+        if not self.shares_cache:
+            shapes["dkv"] = (self.width, self.hidden)
+            shapes["dkv_norm"] = (self.rank,)
+        return shapes
+
+    def load(self, tensors):
+        mats = [tensors["q"]] if self.shares_cache else [tensors["q"], tensors["dkv"]]
+        if len({m.dtype for m in mats}) != 1:
+            raise ValueError("latent_attention: q and dkv matrices must be stored in one dtype")
+        self.proj = Linear(mats)
+        self.dkv_norm = None if self.shares_cache else tensors["dkv_norm"].contiguous()
+        self.uk_t = tensors["uk"].view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.uv = tensors["uv"].view(self.heads, self.vdim, self.rank).contiguous()
+        self.o = Linear([tensors["o"]])
+
+    def reserve(self, limits):
+        for lin in (self.proj, self.o):
+            if lin is not None:
+                lin.reserve(self.ctx.dtype, limits.max_tokens)
+
+    def forward(self, h, out, step, cache):
+        n = h.shape[0]
+        dt = self.ctx.dtype
+        ws = step.workspace
+        if cache.writes == self.shares_cache:
+            raise RuntimeError("latent_attention: the run's cache and the layer's shares_cache disagree")
+        cols = self.q_cols if self.shares_cache else self.q_cols + self.width
+        proj = ws.rows("latent_proj", n, cols, dt)
+        self.proj.forward(h, proj)
+        q = ws.rows("latent_q", n, self.heads * self.width, torch.float32)
+        cos, sin = self.position.tables()
+        ops.latent_prep(proj, q, self.heads, self.dim, self.rot, self.rank, self.dkv_norm, self.norm_eps, cos, sin,
+                        step.positions, cache.slots, cache.tensor if cache.writes else None)
+        ops.gemm_simt_batched(proj, self.dim + self.rot, self.uk_t, q, self.width)
+        mix = ws.rows("latent_mix", n, self.heads * self.rank, torch.float32)
+        ops.latent_attention(q, mix, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
+                             self.rank, self.rot, self.window, self.scale, cache.page_size)
+        ctx = ws.rows("latent_ctx", n, self.heads * self.vdim, dt)
+        ops.gemm_simt_batched(mix, self.rank, self.uv, ctx, self.vdim)
+        return self.o.forward(ctx, out, defer=True)

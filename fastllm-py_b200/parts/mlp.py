@@ -1,8 +1,10 @@
-"""SwiGLU feed-forward: down( silu(gate(h)) * up(h) ), no biases.
+"""Gated feed-forward: down( act(gate(h)) * up(h) ), no biases; SwiGLU when act is silu.
 
 fastllm_py/model.py:432-435 with the activation of
 fastllm_py/kernels/ops.py:157-163: g / (1 + exp(-g)) * u in float.  gate and up
-are stacked into one matrix so that one product serves both."""
+are stacked into one matrix so that one product serves both.  Other activations
+(`activation`: "relu", "gelu_tanh") take the unfused path: product, then one
+activation kernel."""
 from __future__ import annotations
 
 from ..native import ops
@@ -11,15 +13,18 @@ from .linear import Linear
 from .registry import register_part
 
 
+@register_part("feed_forward", "glu")
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
-    """params: hidden_size, intermediate_size.  tensors: gate, up [I, hidden], down [hidden, I]."""
+    """params: hidden_size, intermediate_size, activation ("silu").  tensors: gate, up [I, hidden], down [hidden, I]."""
     category = "feed_forward"
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        self.activation = spec.params.get("activation", "silu")
+        ops.activation_code(self.activation)
         self.gate_up = None
         self.down = None
 
@@ -42,11 +47,14 @@ class SwiGLU(Part):
         n = h.shape[0]
         dt = self.ctx.dtype
         act = step.workspace.rows("ffn_act", n, self.inter, dt)
-        if self.gate_up.forward_gated(h, act):               # product and activation in one kernel
+        silu = self.activation == "silu"
+        if silu and self.gate_up.forward_gated(h, act):      # product and activation in one kernel
             return self.down.forward(act, out, defer=True)
         gu = step.workspace.rows("gate_up", n, 2 * self.inter, dt)
-        partial = self.gate_up.forward(h, gu, defer=True)
-        if partial is None:
+        partial = self.gate_up.forward(h, gu, defer=silu)
+        if not silu:
+            ops.glu(gu, act, self.activation)
+        elif partial is None:
             ops.swiglu(gu, act)
         else:
             ops.swiglu_partial(partial, act)

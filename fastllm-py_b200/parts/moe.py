@@ -1,0 +1,77 @@
+"""Routed experts: a feed-forward that sends each token to a few of many small
+gated feed-forwards and adds their outputs up with the router's weights.
+
+Router: logits z = W_r h in float; scores s = sigmoid(z) (`score`: "sigmoid" or
+"softmax" over the experts); the `top` experts with the largest s + bias are
+chosen, where the bias (`correction`, a stored vector) steers the choice only;
+the weights are the chosen experts' s, renormalised to sum 1 only if
+`renormalise` says so.  Expert e: W_down,e (act(W_gate,e h) * (W_up,e h)), no
+biases.  The experts' matrices are stacked at load into [experts, 2 ff, hidden]
+(gate rows, then up rows) and [experts, hidden, ff].
+"""
+from __future__ import annotations
+
+import torch
+
+from ..native import ops
+from .base import Part
+from .registry import register_part
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(Part):
+    """params: hidden_size, experts, top, expert_ff, activation ("silu"), score ("sigmoid"), renormalise (False),
+    choice_bias (True: a `correction` tensor is added to the scores for the choice).
+    tensors: router [experts, hidden], correction [experts] (if choice_bias), and per expert i
+    gate.i, up.i [ff, hidden], down.i [hidden, ff]."""
+    category = "feed_forward"
+    native_libraries = ("moe",)
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        p = spec.params
+        self.hidden, self.experts, self.top = int(p["hidden_size"]), int(p["experts"]), int(p["top"])
+        self.ff = int(p["expert_ff"])
+        self.activation = p.get("activation", "silu")
+        ops.activation_code(self.activation)
+        self.score = p.get("score", "sigmoid")
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"routed_experts: score {self.score!r} is not 'sigmoid' or 'softmax'")
+        self.renormalise = bool(p.get("renormalise", False))
+        self.choice_bias = bool(p.get("choice_bias", True))
+        if not 1 <= self.top <= self.experts:
+            raise ValueError(f"routed_experts: top {self.top} of {self.experts} experts")
+        if self.hidden * 4 > 48 * 1024:
+            raise ValueError(f"routed_experts: hidden size {self.hidden} exceeds the kernels' 12288")
+
+    def weight_shapes(self):
+        shapes = {"router": (self.experts, self.hidden)}
+        if self.choice_bias:
+            shapes["correction"] = (self.experts,)
+        for e in range(self.experts):
+            shapes[f"gate.{e}"] = (self.ff, self.hidden)
+            shapes[f"up.{e}"] = (self.ff, self.hidden)
+            shapes[f"down.{e}"] = (self.hidden, self.ff)
+        return shapes
+
+    def load(self, tensors):
+        self.router = tensors["router"].contiguous()
+        self.correction = tensors["correction"].contiguous() if self.choice_bias else None
+        first = tensors["gate.0"]
+        self.gate_up = torch.empty((self.experts, 2 * self.ff, self.hidden), dtype=first.dtype, device=first.device)
+        self.down = torch.empty((self.experts, self.hidden, self.ff), dtype=first.dtype, device=first.device)
+        for e in range(self.experts):                    # expert by expert: no second copy of all of them
+            self.gate_up[e, :self.ff] = tensors[f"gate.{e}"]
+            self.gate_up[e, self.ff:] = tensors[f"up.{e}"]
+            self.down[e] = tensors[f"down.{e}"]
+
+    def forward(self, h, out, step):
+        n = h.shape[0]
+        ws = step.workspace
+        chosen = ws.rows("moe_chosen", n, self.top, torch.int32)
+        weights = ws.rows("moe_weights", n, self.top, torch.float32)
+        ops.moe_route(h, self.router, self.correction, chosen, weights, self.top, self.score == "softmax",
+                      self.renormalise)
+        act = ws.rows("moe_act", n, self.top * self.ff, torch.float32)
+        ops.moe_experts(h, self.gate_up, self.down, chosen, weights, act, out, self.activation)
+        return None

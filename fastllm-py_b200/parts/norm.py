@@ -15,6 +15,7 @@ class RMSNorm(Part):
     """params: size, eps.  tensors: weight [size]."""
     category = "norm"
     takes_partial = True                 # split-K partial sums are added while the row is read
+    takes_post_norm = True               # a pending sum that passes another RMSNorm first: one kernel does both
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -32,6 +33,13 @@ class RMSNorm(Part):
         """Norm the residual stream into `out`, adding the pending sum first.
         With `rows` (int32 indices) only those rows are normed, into out[0..m), and the
         pending sum (a tensor then: `ResidualStream.norm_into` sees to it) stays pending."""
+        post = getattr(stream, "pending_norm", None)
+        if stream.pending is not None and post is not None:
+            # x += post(pending); out = self(x): the layer norms the sublayer's output before adding it
+            ops.sandwich_norm(stream.x, stream.pending, post.weight, post.eps, self.weight, self.eps, out, rows)
+            if rows is None:
+                stream.pending = stream.pending_norm = None
+            return
         if stream.pending is not None:
             if not isinstance(stream.pending, torch.Tensor):         # split-K partial sums
                 if rows is not None:
@@ -44,3 +52,8 @@ class RMSNorm(Part):
                 stream.pending = None
         else:
             ops.rmsnorm(stream.x, self.weight, out, self.eps, rows)
+
+    def add_normed(self, stream):
+        """stream.x += rmsnorm(stream.pending) * weight: this part as the norm of a sublayer's output."""
+        ops.sandwich_norm(stream.x, stream.pending, self.weight, self.eps, None, 0.0, None)
+        stream.pending = stream.pending_norm = None

@@ -31,7 +31,7 @@ class LayerSpec:
     """A layer = an arrangement (`block`) of a mixer, a feed-forward and norms."""
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None      # None: the layer is a mixer only (blocks that allow it)
     norms: dict            # role in the block -> PartSpec
 
 
@@ -89,7 +89,8 @@ class ModelPlan:
         visit(self.embedding)
         for layer in self.layers:
             visit(layer.mixer)
-            visit(layer.feed_forward)
+            if layer.feed_forward is not None:
+                visit(layer.feed_forward)
             for spec in layer.norms.values():
                 visit(spec)
         visit(self.final_norm)

@@ -20,7 +20,9 @@ from .registry import register_part
 
 @register_part("position", "rotary")
 class Rotary(Part):
-    """params: rot_dim (even, <= head_dim), theta, scaling: None | ("linear", factor)."""
+    """params: rot_dim (even, <= head_dim), theta, scaling: None | ("linear", factor), exact (False: the
+    frequencies and angles are rounded to float32 before cos and sin, as above; True: they are formed in
+    float64 and only cos and sin are rounded, for models specified by the formula rather than by float32 code)."""
     category = "position"
 
     def __init__(self, spec, ctx):
@@ -28,6 +30,7 @@ class Rotary(Part):
         self.rot_dim = int(spec.params["rot_dim"])
         self.theta = float(spec.params["theta"])
         self.scaling = spec.params.get("scaling")
+        self.exact = bool(spec.params.get("exact", False))
         if self.rot_dim % 2:
             raise ValueError(f"rotary: rot_dim {self.rot_dim} must be even")
         if self.scaling is not None and self.scaling[0] != "linear":
@@ -35,7 +38,17 @@ class Rotary(Part):
 
     def tables(self):
         """(cos, sin) on the device, shared by all parts with the same constants."""
-        key = ("rotary", self.rot_dim, self.theta, self.scaling, self.ctx.max_positions)
+        key = ("rotary", self.rot_dim, self.theta, self.scaling, self.ctx.max_positions, self.exact)
+        if key not in self.ctx.shared and self.exact:
+            d = self.rot_dim
+            inv_freq = self.theta ** (-np.arange(0, d, 2, dtype=np.float64) / d)
+            pos = np.arange(self.ctx.max_positions, dtype=np.float64)
+            if self.scaling is not None:
+                pos = pos / float(self.scaling[1])
+            ang = pos[:, None] * inv_freq[None, :]
+            cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(self.ctx.device)
+            sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(self.ctx.device)
+            self.ctx.shared[key] = (cos.contiguous(), sin.contiguous())
         if key not in self.ctx.shared:
             d = self.rot_dim
             inv_freq = 1.0 / (self.theta ** (np.arange(0, d, 2, dtype=np.float32) / d))
