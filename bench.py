@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--workload decode|serve|67b]
+                    [--workload decode|serve|67b|tables|hybrid]
 
 The default run is the DeepSeek-LLM-7B sized model (30 layers, hidden 4096,
 32 heads, head size 128, feed-forward 11008, vocabulary 102400) with random
@@ -40,6 +40,8 @@ Two more workloads, each printing one line of its own:
              token, time between tokens, how often a request was pushed out;
   --workload tables  the headline model at other sizes: prompt steps of 128 to 8192 tokens, a 4096-token
              prompt in portions of 512, decode steps over a grid of batch sizes and context lengths;
+  --workload hybrid  the Tigitar hybrid (gated delta rule + latent attention + routed experts) at two widths
+                     beside the dense decoder of equal width and depth: prompt and decode steps
   --workload 67b     deepseek-llm-67b size (95 layers, hidden 8192, 64 heads over 8 key/value
              heads; 135 GB of weights on the one GPU): a 2048-token prompt step and decode
              steps at batch 1, 8 and 16 with 4000-token contexts, with their roofline fractions.
@@ -502,6 +504,156 @@ def run_tables(args, warmup):
     return 0
 
 
+HYBRID_SIZES = {
+    # a hybrid of gated-delta-rule and latent-attention layers at widths a small production model has, and
+    # the dense Llama-style decoder of the same width, depth and (active) feed-forward size beside it
+    "w2048": dict(width=2048, vocab=32256, layers=8, delta=dict(heads=16, kv_heads=8, dim=128, vdim=128, conv=4),
+                  latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=1024),
+                  dense_ff=5504, experts=32, top=4, expert_ff=1408,
+                  llama=dict(num_heads=16, num_kv_heads=16, head_dim=128, intermediate_size=5504)),
+    "w4096": dict(width=4096, vocab=32256, layers=4, delta=dict(heads=32, kv_heads=16, dim=128, vdim=128, conv=4),
+                  latent=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=2048),
+                  dense_ff=11008, experts=16, top=2, expert_ff=5504,
+                  llama=dict(num_heads=32, num_kv_heads=32, head_dim=128, intermediate_size=11008)),
+}
+
+
+def hybrid_config(size):
+    """A Tigitar configuration of `size`: layers cycle through delta + dense, latent attention + experts,
+    delta + experts, latent attention reading the earlier layer's cache + dense."""
+    from fastllm_py_b200.config.tigitar import (DeltaMixerConfig, DenseFeedForwardConfig, LatentAttentionConfig,
+                                                RoutedFeedForwardConfig, TigitarConfig, TigitarLayerConfig)
+
+    z = HYBRID_SIZES[size]
+    d, a = z["delta"], z["latent"]
+    delta = DeltaMixerConfig(d["heads"], d["kv_heads"], d["dim"], d["vdim"], d["conv"])
+
+    def latent(kv_from):
+        return LatentAttentionConfig(a["heads"], a["dim"], a["rot_dim"], a["vdim"], a["kv_rank"],
+                                     (a["dim"] + a["rot_dim"]) ** -0.5, 10000.0, a["window"], kv_from)
+
+    dense, routed = DenseFeedForwardConfig(z["dense_ff"]), RoutedFeedForwardConfig(z["experts"], z["top"], z["expert_ff"])
+    layers, owner = [], None
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind == 0:
+            layers.append(TigitarLayerConfig("delta", delta, dense))
+        elif kind == 1:
+            owner = i
+            layers.append(TigitarLayerConfig("latent_attention", latent(None), routed))
+        elif kind == 2:
+            layers.append(TigitarLayerConfig("delta", delta, routed))
+        else:
+            layers.append(TigitarLayerConfig("latent_attention", latent(owner), dense))
+    return TigitarConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, logit_softcap=30.0, layers=tuple(layers))
+
+
+def hybrid_decode_bytes(cfg, batch, context):
+    """Bytes a decode step of the hybrid has to move: the weights it uses once in bfloat16 (of the experts,
+    those that `batch` tokens can reach), every request's delta-rule states read and written in float, and
+    the latent cache rows inside each window."""
+    from fastllm_py_b200.config.tigitar import DeltaMixerConfig, RoutedFeedForwardConfig
+
+    w, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer.mixer
+        if isinstance(m, DeltaMixerConfig):
+            qk, hv = m.kv_heads * m.dim, m.heads * m.vdim
+            total += 2 * w * (2 * qk + 2 * hv + 2 * m.heads) + 2 * hv * w
+            total += batch * 2 * 4 * (m.heads * m.vdim * m.dim + (m.conv - 1) * (2 * qk + hv))
+        else:
+            rows = (0 if m.kv_from is not None else m.kv_rank + m.rot_dim)
+            total += 2 * w * (m.heads * (m.dim + m.rot_dim) + rows) + 2 * m.heads * m.kv_rank * (m.dim + m.vdim)
+            total += 2 * m.heads * m.vdim * w
+            total += batch * min(context, m.window or context) * (m.kv_rank + m.rot_dim) * 2
+        f = layer.mlp
+        if isinstance(f, RoutedFeedForwardConfig):
+            total += 2 * 3 * w * f.ff * min(f.experts, batch * f.top) + 2 * w * f.experts
+        elif f is not None:
+            total += 2 * 3 * w * f.ff
+    return total + 2 * w * cfg.vocab + 2 * batch * w
+
+
+def hybrid_prefill_flops(cfg, tokens):
+    """Matrix-product FLOPs of a prompt step (projections, feed-forwards, attention in latent space over the
+    window, head); the delta rule's recurrence adds 6 dim vdim per head and token."""
+    from fastllm_py_b200.config.tigitar import DeltaMixerConfig, RoutedFeedForwardConfig
+
+    w, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer.mixer
+        if isinstance(m, DeltaMixerConfig):
+            qk, hv = m.kv_heads * m.dim, m.heads * m.vdim
+            total += 2 * tokens * w * (2 * qk + 3 * hv + 2 * m.heads) + tokens * m.heads * 6 * m.dim * m.vdim
+        else:
+            rows = (0 if m.kv_from is not None else m.kv_rank + m.rot_dim)
+            total += 2 * tokens * (w * (m.heads * (m.dim + m.rot_dim) + rows) + m.heads * m.kv_rank * (m.dim + m.vdim)
+                                   + m.heads * m.vdim * w)
+            seen = sum(min(p + 1, m.window or p + 1) for p in range(tokens))
+            total += 2 * m.heads * seen * (2 * m.kv_rank + m.rot_dim)
+        f = layer.mlp
+        if isinstance(f, RoutedFeedForwardConfig):
+            total += 2 * tokens * (3 * w * f.ff * f.top + w * f.experts)
+        elif f is not None:
+            total += 2 * tokens * 3 * w * f.ff
+    return total + 2 * w * cfg.vocab
+
+
+def run_hybrid(args, warmup):
+    """The hybrid architecture beside the dense decoder of equal width and depth, one JSON line: prompt
+    steps of 512 and 2048 tokens and decode steps at batch 1 and 8 over 2048-token contexts, with each
+    model's fraction of its own roofline (measured tensor peak for prompts, measured copy bandwidth for
+    decode steps)."""
+    from fastllm_py_b200 import LlamaConfig, Model
+
+    pk = peaks()
+    steps = max(8, min(args.steps, 32))
+    out = {}
+    sampler = ClockSampler().start()
+    sampler.__enter__()
+    for size in (args.size.split(",") if args.size else list(HYBRID_SIZES)):
+        z = HYBRID_SIZES[size]
+        hybrid = hybrid_config(size)
+        llama = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                            num_layers=z["layers"], hidden_size=z["width"], vocab_size=z["vocab"], rope_theta=10000.0,
+                            rms_norm_eps=1e-6, max_position_embeddings=4096, **z["llama"])
+        res = {}
+        for name, cfg in (("hybrid", hybrid), ("dense", llama)):
+            model = Model.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=8 * (CONTEXT + 256),
+                                      max_requests=8, max_batched_tokens=2048, max_model_len=4096,
+                                      cuda_graph=not args.no_graph)
+            r = {"prompt_step": {}, "decode": {}}
+            for t in (512, 2048):
+                ms, _ = time_prefill(model, t, 8, 3)
+                flops = hybrid_prefill_flops(cfg, t) if name == "hybrid" else prefill_flops(cfg, t)
+                r["prompt_step"][str(t)] = {"ms": round(ms, 3), "value": round(t * 1000.0 / ms, 1),
+                                            "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            for b in (1, 8):
+                v, ms, launches, _ = time_decode(model, b, steps, warmup, CONTEXT)
+                ctx = CONTEXT + warmup + (steps + 1) / 2
+                nbytes = hybrid_decode_bytes(cfg, b, ctx) if name == "hybrid" else decode_bytes(cfg, b, ctx)
+                r["decode"][f"{b}x{CONTEXT}"] = {"ms_per_step": round(ms, 3), "value": round(v, 1),
+                                                 "launches_per_step": launches // steps,
+                                                 "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+            res[name] = r
+            del model
+            import gc
+
+            import torch
+            gc.collect()
+            torch.cuda.empty_cache()
+        out[size] = res
+    sampler.__exit__()
+    print(json.dumps({
+        "metric": "prompt and decode steps of the Tigitar hybrid beside the dense decoder of equal size, bf16",
+        "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": steps, "warmup": warmup,
+        "config": {"sizes": {k: {kk: vv for kk, vv in HYBRID_SIZES[k].items()} for k in out}, "page_size": 16,
+                   "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"],
+                   "cuda_graph": not args.no_graph},
+        "sizes": out, "clocks": sampler.summary()}))
+    return 0
+
+
 def reference_cpu_path(ref_root, layers=1, context=256, decode_tokens=8):
     """fastllm-py's own NumPy model code (its CPU device, float32) timed at DeepSeek-LLM-7B layer
     sizes: `layers` of the 30 layers, one sequence (that path has no batch), a `context`-token
@@ -638,9 +790,10 @@ def main():
                     help="run fewer layers of the same sizes (the line names both numbers)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables", "hybrid"],
                     help="decode: the headline line (DeepSeek-LLM-7B size); serve: continuous batching at "
                          "deepseek-coder-1.3b size; 67b: prompt and decode steps at deepseek-llm-67b size")
+    ap.add_argument("--size", default="", help="hybrid: which sizes (w2048,w4096; default both)")
     ap.add_argument("--requests", type=int, default=128, help="serve: how many requests")
     ap.add_argument("--rate", type=float, default=16.0, help="serve: mean arrivals a second")
     ap.add_argument("--reference-cpu", action="store_true",
@@ -659,6 +812,8 @@ def main():
         return run_67b(args, warmup)
     if args.workload == "tables":
         return run_tables(args, warmup)
+    if args.workload == "hybrid":
+        return run_hybrid(args, warmup)
     args.layers = args.layers or MODEL_7B["num_layers"]
 
     import torch

@@ -79,12 +79,11 @@ def main(argv=None) -> int:
                        max_tokens=args.max_tokens or max(4096, 2 * (n_prompt + args.n_new)),
                        max_model_len=longest, cuda_graph=not args.no_graph, max_requests=4)
     cfg = model.cfg
-    print(f"[load {time.time() - t0:.1f}s] {cfg.architecture}: {cfg.num_layers}L hidden={cfg.hidden_size} "
-          f"heads={cfg.num_heads}/{cfg.num_kv_heads} dtype={model.engine_config.dtype}")
+    print(f"[load {time.time() - t0:.1f}s] {cfg.summary()} dtype={model.engine_config.dtype}")
     if ids is None:
         import numpy as np
 
-        ids = np.random.default_rng(args.seed or 0).integers(0, cfg.vocab_size, args.random_prompt).tolist()
+        ids = np.random.default_rng(args.seed or 0).integers(0, model.plan.vocab_size, args.random_prompt).tolist()
 
     stop = [int(x) for x in args.stop_ids.split(",") if x.strip()]
     t0 = time.time()
@@ -134,5 +133,5 @@ def make_model_main(argv=None) -> int:
     arch = architecture_of(raw)
     config = arch.config_class.from_hf(raw)
     folder = write_model_folder(config, args.out, args.seed, args.std, args.norm_std, args.dtype)
-    print(f"wrote {folder}/config.json and model.safetensors ({raw.get('architectures', ['?'])[0]}, seed {args.seed})")
+    print(f"wrote {folder}/config.json and model.safetensors ({arch.name}, seed {args.seed})")
     return 0

@@ -100,6 +100,11 @@ class LlamaConfig:
             tie_word_embeddings=r.boolean("tie_word_embeddings", default=False),
         )
 
+    def summary(self) -> str:
+        """One line for a load message."""
+        return (f"{self.architecture}: {self.num_layers}L hidden={self.hidden_size} "
+                f"heads={self.num_heads}/{self.num_kv_heads}")
+
     def to_hf(self) -> dict:
         """The config.json that reads back as this configuration."""
         out = {

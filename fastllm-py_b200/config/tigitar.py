@@ -184,6 +184,13 @@ class TigitarConfig:
                    logit_softcap=r.number("logit_softcap", default=None) if raw.get("logit_softcap") is not None
                    else None, layers=tuple(layers))
 
+    def summary(self) -> str:
+        """One line for a load message."""
+        kinds = [layer.type for layer in self.layers]
+        routed = sum(isinstance(layer.mlp, RoutedFeedForwardConfig) for layer in self.layers)
+        return (f"Tigitar: {len(kinds)}L width={self.width} ({kinds.count('delta')} delta, "
+                f"{kinds.count('latent_attention')} latent attention; {routed} with routed experts)")
+
     def to_hf(self) -> dict:
         """The config.json that reads back as this configuration."""
         out = {"architecture": "Tigitar", "layers": [layer.to_raw() for layer in self.layers],

@@ -154,3 +154,247 @@ FL_API int fl_moe_experts(const void* h, int dtype, long h_ld, const void* w_gu,
                          (const TW*)w_down, chosen, weights, (T*)out, out_ld, width, ff, top)));
     return 0;
 }
+
+// ----------------------------------------------------------------- many tokens: grouped products
+// With many tokens the per-token kernels above would read each expert's matrices once per token.  Here
+// the (token, choice) pairs are ordered by expert, each expert's rows padded to whole tiles of 64, and
+// two tensor-core products run over the tiles: a tile's rows share one expert's matrix.
+//
+//   moe_sort        one block: counts per expert, padded offsets, row -> pair, pair -> row, tile -> expert
+//   moe_group_mma   bfloat16 mma.sync m16n8k16, 64 rows x 128 weight rows per block, K in steps of 32 through
+//                   a two-stage cp.async ring.  GATED: the 128 weight rows are 64 gate rows and the 64 up rows
+//                   of the same features, A rows are gathered token rows, the epilogue writes act(g) * u
+//                   (bfloat16, in row order); else A is that buffer and the output float [rows, width]
+//   moe_combine     out[t] = sum_k weight[t, k] * y[row of pair (t, k)], in order of choice
+//
+// A row's sums do not depend on the other rows of its tile, so the order of rows within an expert (it
+// comes from atomics) does not show in the results.
+#define MOE_TM 64
+
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ chosen, int n_pairs, int experts,
+                                                       int* __restrict__ row_pair, int* __restrict__ pair_row,
+                                                       int* __restrict__ tile_expert, int* __restrict__ n_tiles_out,
+                                                       int max_tiles) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ int sort_s[];                      // [experts] counts -> cursors, [experts + 1] first rows
+    int* count = sort_s;
+    int* first = sort_s + experts;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&count[chosen[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            first[e] = at;
+            const int tiles = (count[e] + MOE_TM - 1) / MOE_TM;
+            for (int i = 0; i < tiles; ++i) tile_expert[at / MOE_TM + i] = e;
+            at += tiles * MOE_TM;
+            count[e] = 0;
+        }
+        first[experts] = at;
+        *n_tiles_out = at / MOE_TM;
+    }
+    __syncthreads();
+    const int total = first[experts];
+    for (int r = threadIdx.x; r < max_tiles * MOE_TM; r += blockDim.x) row_pair[r] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = chosen[p];
+        const int r = first[e] + atomicAdd(&count[e], 1);
+        row_pair[r] = p;
+        pair_row[p] = r;
+    }
+    (void)total;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+#define MOE_BK 32
+#define MOE_PITCH 40             // bfloat16 elements between rows of a staged tile: ldmatrix without bank conflicts
+
+// grid: (tiles of rows, blocks of 64 features (GATED) or 128 columns).  K % 32 == 0, rows 16-byte aligned.
+template <bool GATED>
+__global__ void __launch_bounds__(256) moe_group_mma_kernel(
+    const bf16* __restrict__ a, long a_ld, const bf16* __restrict__ w, int n_out, int K, const int* __restrict__ row_pair,
+    const int* __restrict__ tile_expert, const int* __restrict__ n_tiles, int top, bf16* __restrict__ act_out,
+    float* __restrict__ y_out, long out_ld, int act) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ __align__(16) bf16 a_s[2][MOE_TM][MOE_PITCH];
+    __shared__ __align__(16) bf16 w_s[2][128][MOE_PITCH];
+    __shared__ int pair_s[MOE_TM];
+    const int tile = blockIdx.x;
+    if (tile >= *n_tiles) return;
+    const int e = tile_expert[tile];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 2, wn = warp & 3;                    // 2 x 4 warps: 32 rows x (GATED: 16 + 16, else 32) columns
+    if (tid < MOE_TM) pair_s[tid] = row_pair[tile * MOE_TM + tid];
+    __syncthreads();
+    // sources of this thread's 16-byte pieces of a stage: one of A (64 rows x 4), two of W (128 rows x 4)
+    const int ar = tid >> 2, ac = (tid & 3) * 8;
+    const bf16* a_src;
+    if (GATED) {
+        const int pair = pair_s[ar];
+        a_src = a + (long)(pair < 0 ? 0 : pair / top) * a_ld + ac;
+    } else {
+        a_src = a + ((long)tile * MOE_TM + ar) * a_ld + ac;
+    }
+    const bf16* w_src[2];
+    bool w_ok[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int wr = (tid >> 2) + i * 64;
+        long row;                                               // row of this expert's matrix
+        if (GATED) {
+            const int f = blockIdx.y * 64 + (wr & 63);          // rows 0..63 gate features, 64..127 their up rows
+            w_ok[i] = f < n_out;
+            row = (long)e * 2 * n_out + (wr < 64 ? 0 : n_out) + (w_ok[i] ? f : 0);
+        } else {
+            const int c = blockIdx.y * 128 + wr;
+            w_ok[i] = c < n_out;
+            row = (long)e * n_out + (w_ok[i] ? c : 0);
+        }
+        w_src[i] = w + row * K + ac;
+    }
+    auto stage = [&](int buf, int k0) {
+        cp_async16(&a_s[buf][ar][ac], a_src + k0);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) cp_async16(&w_s[buf][(tid >> 2) + i * 64][ac], w_src[i] + k0);
+        cp_async_commit();
+    };
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.0f;
+    const int n_k = K / MOE_BK;
+    stage(0, 0);
+    for (int kb = 0; kb < n_k; ++kb) {
+        const int buf = kb & 1;
+        if (kb + 1 < n_k) {
+            stage(buf ^ 1, (kb + 1) * MOE_BK);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < MOE_BK; ks += 16) {
+            unsigned af[2][4], bfr[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const bf16* p = &a_s[buf][wm * 32 + i * 16 + (lane & 15)][ks + (lane >> 4) * 8];
+                const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(af[i][0]), "=r"(af[i][1]), "=r"(af[i][2]), "=r"(af[i][3]) : "r"(s));
+            }
+#pragma unroll
+            for (int j2 = 0; j2 < 2; ++j2) {
+                // GATED: column blocks 0, 1 are 16 gate features, 2, 3 the same features' up rows
+                const int n0 = GATED ? (j2 * 64 + wn * 16) : (wn * 32 + j2 * 16);
+                const bf16* p = &w_s[buf][n0 + (lane & 7) + (lane >> 4) * 8][ks + ((lane >> 3) & 1) * 8];
+                const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(bfr[j2 * 2][0]), "=r"(bfr[j2 * 2][1]), "=r"(bfr[j2 * 2 + 1][0]), "=r"(bfr[j2 * 2 + 1][1])
+                             : "r"(s));
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[i][j][0]), "+f"(acc[i][j][1]), "+f"(acc[i][j][2]), "+f"(acc[i][j][3])
+                                 : "r"(af[i][0]), "r"(af[i][1]), "r"(af[i][2]), "r"(af[i][3]), "r"(bfr[j][0]), "r"(bfr[j][1]));
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm * 32 + i * 16 + (lane >> 2) + half * 8;
+            const long row = (long)tile * MOE_TM + r;
+            if (GATED) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int f = blockIdx.y * 64 + wn * 16 + j * 8 + (lane & 3) * 2 + c;
+                        if (f < n_out)
+                            act_out[row * out_ld + f] = __float2bfloat16_rn(moe_act(acc[i][j][half * 2 + c], act) *
+                                                                            acc[i][j + 2][half * 2 + c]);
+                    }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int col = blockIdx.y * 128 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
+                        if (col < n_out) y_out[row * out_ld + col] = acc[i][j][half * 2 + c];
+                    }
+            }
+        }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, long y_ld, const int* __restrict__ pair_row,
+                                                          const float* __restrict__ weights, T* __restrict__ out, long out_ld,
+                                                          int width, int top) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
+        float sum = 0.0f;
+        for (int k = 0; k < top; ++k) sum += weights[(long)t * top + k] * y[(long)pair_row[(long)t * top + k] * y_ld + c];
+        out[(long)t * out_ld + c] = from_f32<T>(sum);
+    }
+}
+
+// Rows of the ordered buffers a step of n_tokens needs: every expert may end with a partly filled tile.
+FL_API long fl_moe_group_rows(int n_tokens, int top, int experts) {
+    return (((long)n_tokens * top + MOE_TM - 1) / MOE_TM + experts) * MOE_TM;
+}
+
+// Does the grouped path take this problem?  (bfloat16 everywhere, K of both products a multiple of 32.)
+FL_API int fl_moe_group_takes(int dtype, int w_dtype, int width, int ff) {
+    return dtype == FL_BF16 && w_dtype == FL_BF16 && width % MOE_BK == 0 && ff % MOE_BK == 0;
+}
+
+// ints: row_pair [rows] | pair_row [n_tokens * top] | tile_expert [rows / 64] | n_tiles [1];
+// act: bfloat16 [rows, ff]; y: float [rows, width].
+FL_API int fl_moe_experts_grouped(const void* h, long h_ld, const void* w_gu, const void* w_down, const int* chosen,
+                                  const float* weights, int* ints, void* act, float* y, void* out, long out_ld,
+                                  int n_tokens, int width, int ff, int top, int experts, int act_code, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const long rows = fl_moe_group_rows(n_tokens, top, experts);
+    const int max_tiles = (int)(rows / MOE_TM);
+    int* row_pair = ints;
+    int* pair_row = row_pair + rows;
+    int* tile_expert = pair_row + (long)n_tokens * top;
+    int* n_tiles = tile_expert + max_tiles;
+    if ((size_t)(2 * experts + 1) * sizeof(int) > 48 * 1024 || ((uintptr_t)h % 16) || (h_ld % 8)) return (int)cudaErrorInvalidValue;
+    int rc = fl_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, chosen,
+                       n_tokens * top, experts, row_pair, pair_row, tile_expert, n_tiles, max_tiles);
+    if (rc) return rc;
+    rc = fl_launch(moe_group_mma_kernel<true>, dim3(max_tiles, (ff + 63) / 64), dim3(256), 0, stream, (const bf16*)h, h_ld,
+                   (const bf16*)w_gu, ff, width, (const int*)row_pair, (const int*)tile_expert, (const int*)n_tiles, top,
+                   (bf16*)act, (float*)nullptr, (long)ff, act_code);
+    if (rc) return rc;
+    rc = fl_launch(moe_group_mma_kernel<false>, dim3(max_tiles, (width + 127) / 128), dim3(256), 0, stream,
+                   (const bf16*)act, (long)ff, (const bf16*)w_down, width, ff, (const int*)row_pair,
+                   (const int*)tile_expert, (const int*)n_tiles, top, (bf16*)nullptr, y, (long)width, act_code);
+    if (rc) return rc;
+    int col_blocks = (width + 255) / 256;
+    if (col_blocks > 8) col_blocks = 8;
+    return fl_launch(moe_combine_kernel<bf16>, dim3(n_tokens, col_blocks), dim3(256), 0, stream, (const float*)y,
+                     (long)width, (const int*)pair_row, weights, (bf16*)out, out_ld, width, top);
+}

@@ -386,6 +386,37 @@ def moe_experts(h, w_gate_up, w_down, chosen, weights, act_buf, out, activation=
               activation_code(activation), _stream()), "moe_experts", 2)
 
 
+def moe_group_rows(n_tokens: int, top: int, experts: int) -> int:
+    """Rows of the expert-ordered buffers for a step of `n_tokens` (every expert's rows end on a tile)."""
+    fn = load_library("moe").fl_moe_group_rows
+    fn.argtypes, fn.restype = [c_int, c_int, c_int], c_long
+    return int(fn(n_tokens, top, experts))
+
+
+def moe_group_takes(h_dtype, w_dtype, width: int, ff: int) -> bool:
+    """Whether the grouped tensor-core path serves these types and sizes."""
+    if h_dtype not in _CODES or w_dtype not in _CODES:
+        return False
+    fn = load_library("moe").fl_moe_group_takes
+    fn.argtypes, fn.restype = [c_int, c_int, c_int, c_int], c_int
+    return bool(fn(_CODES[h_dtype], _CODES[w_dtype], width, ff))
+
+
+def moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, ints, act, y, out, activation="silu"):
+    """The same sum as `moe_experts` for many tokens: pairs ordered by expert, two tensor-core products
+    over tiles of 64 rows, then the weighted sum per token.  All bfloat16; `ints` int32
+    [rows + N * top + rows / 64 + 1], `act` bfloat16 [rows, ff], `y` float32 [rows, width] with
+    rows = moe_group_rows(N, top, experts)."""
+    _require_cuda(h, w_gate_up, w_down, chosen, weights, ints, act, y, out)
+    experts, ff2, width = w_gate_up.shape
+    fn = _fn("moe", "fl_moe_experts_grouped", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
+                                               c_int, c_void_p])
+    _check(fn(_ptr(h), _ld(h), _ptr(w_gate_up), _ptr(w_down), _ptr(chosen), _ptr(weights), _ptr(ints), _ptr(act),
+              _ptr(y), _ptr(out), _ld(out), h.shape[0], width, ff2 // 2, chosen.shape[1], experts,
+              activation_code(activation), _stream()), "moe_experts_grouped", 4)
+
+
 # -------------------------------------------------------------- rope + cache
 
 def rope_kv_write(qkv, n_heads, n_kv_heads, head_dim, rot_dim, cos, sin, positions, slots, cache,

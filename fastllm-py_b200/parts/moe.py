@@ -8,12 +8,19 @@ the weights are the chosen experts' s, renormalised to sum 1 only if
 `renormalise` says so.  Expert e: W_down,e (act(W_gate,e h) * (W_up,e h)), no
 biases.  The experts' matrices are stacked at load into [experts, 2 ff, hidden]
 (gate rows, then up rows) and [experts, hidden, ff].
+
+Two ways through the experts.  Few tokens (decode steps): one launch over
+(token, choice) pairs, each streaming its expert's rows; the matrices are read
+about once and the step is bound by that.  Many tokens in bfloat16: the pairs
+are ordered by expert on the device and two tensor-core products run over tiles
+of 64 rows that share an expert (`GROUP_FROM` pairs and up).  Neither path asks
+the host anything, so steps with this part can be captured.
 """
 from __future__ import annotations
 
 import torch
 
-from ..native import ops
+from ..native import ops, scratch
 from .base import Part
 from .registry import register_part
 
@@ -26,6 +33,8 @@ class RoutedExperts(Part):
     gate.i, up.i [ff, hidden], down.i [hidden, ff]."""
     category = "feed_forward"
     native_libraries = ("moe",)
+    GROUP_FROM = 128                 # (token, choice) pairs from which the grouped path is taken
+    SCRATCH = "routed experts"
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -65,6 +74,24 @@ class RoutedExperts(Part):
             self.gate_up[e, self.ff:] = tensors[f"up.{e}"]
             self.down[e] = tensors[f"down.{e}"]
 
+    def _grouped(self, dtype) -> bool:
+        return ops.moe_group_takes(dtype, self.gate_up.dtype, self.hidden, self.ff)
+
+    def _group_buffers(self, n, device):
+        """(ints, act, y) of the grouped path for n tokens, carved out of one scratch buffer."""
+        rows = ops.moe_group_rows(n, self.top, self.experts)
+        n_ints = -(-(rows + n * self.top + rows // 64 + 1) // 4) * 4
+        n_act = rows * self.ff // 2
+        buf = scratch.get(device, self.SCRATCH, n_ints + n_act + rows * self.hidden)
+        ints = buf[:n_ints].view(torch.int32)
+        act = buf[n_ints:n_ints + n_act].view(torch.bfloat16).view(rows, self.ff)
+        y = buf[n_ints + n_act:n_ints + n_act + rows * self.hidden].view(rows, self.hidden)
+        return ints, act, y
+
+    def reserve(self, limits):
+        if self.ctx.device.type == "cuda" and self._grouped(self.ctx.dtype):
+            self._group_buffers(limits.max_tokens, self.ctx.device)       # sized now: nothing grows under a graph
+
     def forward(self, h, out, step):
         n = h.shape[0]
         ws = step.workspace
@@ -72,6 +99,10 @@ class RoutedExperts(Part):
         weights = ws.rows("moe_weights", n, self.top, torch.float32)
         ops.moe_route(h, self.router, self.correction, chosen, weights, self.top, self.score == "softmax",
                       self.renormalise)
+        if n * self.top >= self.GROUP_FROM and self._grouped(h.dtype):
+            ints, act, y = self._group_buffers(n, h.device)
+            ops.moe_experts_grouped(h, self.gate_up, self.down, chosen, weights, ints, act, y, out, self.activation)
+            return None
         act = ws.rows("moe_act", n, self.top * self.ff, torch.float32)
         ops.moe_experts(h, self.gate_up, self.down, chosen, weights, act, out, self.activation)
         return None
