@@ -7,7 +7,7 @@
 // are per head and token.  The read-out sees the token's own write.
 //
 // Four kernels, all float inside:
-//   delta_prep        per token: convolution over the last `taps` inputs (from the step's rows or, before
+//   delta_prep        per token and head: convolution over the last `taps` inputs (from the step's rows or, before
 //                     the portion's start, from the request's saved tail), silu, unit norms, beta, decay
 //   delta_tail        per request: the last taps - 1 raw inputs of the portion become the saved tail
 //   delta_scan        per (request, head, 32 value columns): the recurrence over the portion's tokens,
@@ -23,8 +23,10 @@
 #define DELTA_PARTS 8            // lanes that share one value column
 #define DELTA_COLS 32            // value columns of a block
 
+// One block per (token, unit): a unit is one query head, one key head (dim channels each) or one value
+// head (vdim channels, and the head's beta and decay), so that even a single token spreads over many SMs.
 template <typename T, typename TW>
-__global__ void __launch_bounds__(256) delta_prep_kernel(
+__global__ void __launch_bounds__(128) delta_prep_kernel(
     const T* __restrict__ proj, long ld, const TW* __restrict__ conv_w, const TW* __restrict__ a_log,
     const TW* __restrict__ dt_bias, const float* __restrict__ state, long state_stride, long tail_off,
     const int* __restrict__ tok_req, const int* __restrict__ positions, const int* __restrict__ req_ctx,
@@ -32,14 +34,20 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(
     int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale) {
     pdl_wait();
     pdl_trigger();
-    extern __shared__ float conv_out[];                      // [channels]
-    const int t = blockIdx.x, tid = threadIdx.x;
+    extern __shared__ float conv_out[];                      // [max(dim, vdim)]
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, unit = blockIdx.y, tid = threadIdx.x;
     const int qk_cols = kv_heads * dim, hv = heads * vdim;
     const int channels = 2 * qk_cols + hv;
+    const bool is_v = unit >= 2 * kv_heads;
+    const int first = is_v ? 2 * qk_cols + (unit - 2 * kv_heads) * vdim : unit * dim;
+    const int count = is_v ? vdim : dim;
     const int r = tok_req[t], pos = positions[t], ctx = req_ctx[r];
     const float* tail = state + (long)req_slot[r] * state_stride + tail_off;
     const T* row = proj + (long)t * ld;
-    for (int c = tid; c < channels; c += blockDim.x) {
+    float ss = 0.0f;
+    for (int i = tid; i < count; i += blockDim.x) {
+        const int c = first + i;
         float acc = 0.0f;
         for (int back = taps - 1; back >= 0; --back) {        // oldest input first
             const int p = pos - back;
@@ -48,28 +56,25 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(
                                      : tail[(long)(p - ctx + taps - 1) * channels + c];
             acc += to_f32<TW>(conv_w[(long)c * taps + (taps - 1 - back)]) * x;
         }
-        conv_out[c] = acc / (1.0f + expf(-acc));
+        const float y = acc / (1.0f + expf(-acc));
+        conv_out[i] = y;
+        ss += y * y;
     }
-    __syncthreads();
-    const int warp = tid >> 5, lane = tid & 31, n_warps = blockDim.x >> 5;
-    float* qk_row = work + (long)t * work_ld;              // work row: q | k | v | beta | decay | o
-    float* v_row = qk_row + 2 * qk_cols;
-    float* bg_row = v_row + hv;
-    for (int hh = warp; hh < 2 * kv_heads; hh += n_warps) {  // query heads, then key heads
-        const float* x = conv_out + hh * dim;
-        float ss = 0.0f;
-        for (int d = lane; d < dim; d += 32) ss += x[d] * x[d];
-        ss = warp_sum(ss);
-        const float f = (hh < kv_heads ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
-        for (int d = lane; d < dim; d += 32) qk_row[hh * dim + d] = x[d] * f;
+    float* out_row = work + (long)t * work_ld;               // work row: q | k | v | beta | decay | o
+    if (!is_v) {
+        ss = block_sum(ss, scratch);
+        const float f = (unit < kv_heads ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
+        for (int i = tid; i < count; i += blockDim.x) out_row[first + i] = conv_out[i] * f;   // each thread its own
+        return;
     }
-    for (int j = tid; j < hv; j += blockDim.x) v_row[j] = conv_out[2 * qk_cols + j];
-    for (int h = tid; h < heads; h += blockDim.x) {
+    for (int i = tid; i < count; i += blockDim.x) out_row[first + i] = conv_out[i];
+    if (tid == 0) {
+        const int h = unit - 2 * kv_heads;
         const float b = to_f32<T>(row[channels + hv + h]);
         const float a = to_f32<T>(row[channels + hv + heads + h]) + to_f32<TW>(dt_bias[h]);
         const float softplus = a > 20.0f ? a : log1pf(expf(a));
-        bg_row[h] = 1.0f / (1.0f + expf(-b));
-        bg_row[heads + h] = expf(-expf(to_f32<TW>(a_log[h])) * softplus);
+        out_row[channels + h] = 1.0f / (1.0f + expf(-b));
+        out_row[channels + heads + h] = expf(-expf(to_f32<TW>(a_log[h])) * softplus);
     }
 }
 
@@ -200,11 +205,12 @@ FL_API int fl_delta_prep(const void* proj, int dtype, long ld, const void* conv_
                          cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int channels = 2 * kv_heads * dim + heads * vdim;
-    if (taps < 1 || heads % kv_heads || n_requests > 65535 || (size_t)channels * sizeof(float) > 48 * 1024)
+    const int units = 2 * kv_heads + heads, widest = dim > vdim ? dim : vdim;
+    if (taps < 1 || heads % kv_heads || n_requests > 65535 || units > 65535 || (size_t)widest * sizeof(float) > 48 * 1024)
         return (int)cudaErrorInvalidValue;
     int rc = 0;
     FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
-        rc = fl_launch(delta_prep_kernel<T, TW>, dim3(n_tokens), dim3(256), (size_t)channels * sizeof(float), stream,
+        rc = fl_launch(delta_prep_kernel<T, TW>, dim3(n_tokens, units), dim3(128), (size_t)widest * sizeof(float), stream,
                        (const T*)proj, ld, (const TW*)conv_w, (const TW*)a_log, (const TW*)dt_bias, (const float*)state,
                        state_stride, tail_off, tok_req, positions, req_ctx, req_slot, work, work_ld, heads, kv_heads,
                        dim, vdim, taps, unit_eps, q_scale)));

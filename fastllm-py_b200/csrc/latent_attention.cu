@@ -20,9 +20,9 @@
 #define LAT_MAX_ACC 8            // value elements per thread: rank <= LAT_TILE * LAT_MAX_ACC
 
 // proj row: heads x [dim plain | rot rotated] queries, then (has_kv) rank latent + rot key elements.
-template <typename T, typename TW>
+template <typename T, typename TW, typename TQ>
 __global__ void __launch_bounds__(256) latent_prep_kernel(
-    const T* __restrict__ proj, long ld, float* __restrict__ q_out, long q_ld, int heads, int dim, int rot, int rank,
+    const T* __restrict__ proj, long ld, TQ* __restrict__ q_out, long q_ld, int heads, int dim, int rot, int rank,
     const TW* __restrict__ norm_w, float eps,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ positions,
     const int* __restrict__ slots, T* __restrict__ cache, int has_kv) {
@@ -33,16 +33,16 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
     const int half = rot / 2;
     const long pos = positions[t];
     const T* row = proj + (long)t * ld;
-    float* q_row = q_out + (long)t * q_ld;
+    TQ* q_row = q_out + (long)t * q_ld;
     const float* cs = cos_t + pos * half;
     const float* sn = sin_t + pos * half;
     for (int idx = tid; idx < heads * half; idx += blockDim.x) {
         const int h = idx / half, i = idx % half;
         const T* p = row + (long)h * (dim + rot) + dim;
-        float* o = q_row + (long)h * (rank + rot) + rank;
+        TQ* o = q_row + (long)h * (rank + rot) + rank;
         const float u = to_f32<T>(p[i]), v = to_f32<T>(p[i + half]);
-        o[i] = u * cs[i] - v * sn[i];
-        o[i + half] = v * cs[i] + u * sn[i];
+        o[i] = from_f32<TQ>(u * cs[i] - v * sn[i]);
+        o[i + half] = from_f32<TQ>(v * cs[i] + u * sn[i]);
     }
     if (!has_kv) return;
     const T* kv = row + (long)heads * (dim + rot);
@@ -62,10 +62,10 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
     }
 }
 
-// q: [n_tokens, heads x (rank + rot)] float; out: [n_tokens, heads x rank] float.
-template <typename T>
+// q: [n_tokens, heads x (rank + rot)]; out: [n_tokens, heads x rank] float.
+template <typename T, typename TQ>
 __global__ void __launch_bounds__(LAT_TILE) latent_attention_kernel(
-    const float* __restrict__ q, long q_ld, float* __restrict__ out, long out_ld, const T* __restrict__ cache,
+    const TQ* __restrict__ q, long q_ld, float* __restrict__ out, long out_ld, const T* __restrict__ cache,
     int page_size, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
     const int* __restrict__ positions, int rank, int rot, int window, float scale) {
     pdl_wait();
@@ -80,8 +80,8 @@ __global__ void __launch_bounds__(LAT_TILE) latent_attention_kernel(
     const int pos = positions[t];
     const int* bt = block_table + (long)tok_req[t] * bt_stride;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const float* qr = q + (long)t * q_ld + (long)h * width;
-    for (int d = tid; d < width; d += LAT_TILE) q_s[d] = qr[d];
+    const TQ* qr = q + (long)t * q_ld + (long)h * width;
+    for (int d = tid; d < width; d += LAT_TILE) q_s[d] = to_f32<TQ>(qr[d]);
     __syncthreads();
     float m = -CUDART_INF_F, l = 0.0f, acc[LAT_MAX_ACC];
 #pragma unroll
@@ -126,30 +126,31 @@ __global__ void __launch_bounds__(LAT_TILE) latent_attention_kernel(
     }
 }
 
-// q_out: [n_tokens, q_ld] floats, heads x [rank | rot]: the rot columns of every head are written here.
-FL_API int fl_latent_prep(const void* proj, int dtype, long ld, float* q_out, long q_ld, int n_tokens, int heads, int dim,
+// q_out: [n_tokens, q_ld] (float or bfloat16), heads x [rank | rot]: the rot columns of every head are written here.
+FL_API int fl_latent_prep(const void* proj, int dtype, long ld, void* q_out, int q_dtype, long q_ld, int n_tokens, int heads, int dim,
                           int rot, int rank,
                           const void* norm_w, int w_dtype, float eps, const float* cos_t, const float* sin_t,
                           const int* positions, const int* slots, void* cache, int has_kv, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rot % 2) return (int)cudaErrorInvalidValue;
-    FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
-        return fl_launch(latent_prep_kernel<T, TW>, dim3(n_tokens), dim3(256), 0, stream, (const T*)proj, ld, q_out, q_ld, heads,
-                         dim, rot, rank, (const TW*)norm_w, eps, cos_t, sin_t, positions, slots, (T*)cache, has_kv)));
+    FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(q_dtype, TQ,
+        return fl_launch(latent_prep_kernel<T, TW, TQ>, dim3(n_tokens), dim3(256), 0, stream, (const T*)proj, ld, (TQ*)q_out,
+                         q_ld, heads, dim, rot, rank, (const TW*)norm_w, eps, cos_t, sin_t, positions, slots, (T*)cache,
+                         has_kv))));
     return 0;
 }
 
 // window <= 0: all earlier tokens.
-FL_API int fl_latent_attention(const float* q, long q_ld, float* out, long out_ld, const void* cache, int cache_dtype,
+FL_API int fl_latent_attention(const void* q, int q_dtype, long q_ld, float* out, long out_ld, const void* cache, int cache_dtype,
                                int page_size, const int* block_table, int bt_stride, const int* tok_req,
                                const int* positions, int n_tokens, int heads, int rank, int rot, int window,
                                float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rank < 1 || rank > LAT_TILE * LAT_MAX_ACC || heads > 65535) return (int)cudaErrorInvalidValue;
     const size_t smem = LAT_TILE * (sizeof(long) + sizeof(float)) + (size_t)(rank + rot) * sizeof(float);
-    FL_DISPATCH(cache_dtype, T,
-        return fl_launch(latent_attention_kernel<T>, dim3(n_tokens, heads), dim3(LAT_TILE), smem, stream, q, q_ld, out,
-                         out_ld, (const T*)cache, page_size, block_table, bt_stride, tok_req, positions, rank, rot,
-                         window, scale));
+    FL_DISPATCH(cache_dtype, T, FL_DISPATCH(q_dtype, TQ,
+        return fl_launch(latent_attention_kernel<T, TQ>, dim3(n_tokens, heads), dim3(LAT_TILE), smem, stream, (const TQ*)q,
+                         q_ld, out, out_ld, (const T*)cache, page_size, block_table, bt_stride, tok_req, positions, rank, rot,
+                         window, scale)));
     return 0;
 }

@@ -1,10 +1,10 @@
 // Routed experts: each token's feed-forward is a weighted sum of a few small gated feed-forwards
 // chosen by a router.
 //
-//   moe_route     per token: logits z = W_r h in float; score s = sigmoid(z) (or a softmax over the
-//                 experts); the `top` experts with the largest s + bias are chosen (the bias steers the
-//                 choice only), ties to the lower index; the weights are the chosen s, optionally
-//                 renormalised to sum 1
+//   moe_pick      per token, from the router's float logits z (a product the caller makes): score
+//                 s = sigmoid(z) (or a softmax over the experts); the `top` experts with the largest
+//                 s + bias are chosen (the bias steers the choice only), ties to the lower index; the
+//                 weights are the chosen s, optionally renormalised to sum 1
 //   moe_gate_up   per (token, choice): act(W_gate[e] h) * (W_up[e] h), one warp per feature
 //   moe_down      per token: sum over its choices, in order of choice, of weight * W_down[e] a
 //
@@ -19,37 +19,30 @@ __device__ __forceinline__ float moe_act(float g, int act) {
     return g / (1.0f + expf(-g));
 }
 
-template <typename T, typename TW>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, long h_ld, const TW* __restrict__ w_router,
-                                                        const TW* __restrict__ bias, int* __restrict__ chosen,
-                                                        float* __restrict__ weights, int width, int experts, int top,
-                                                        int softmax_scores, int renormalise) {
+// One warp per token; z: float logits [n_tokens, experts] (the router's product, made by the caller).
+template <typename TW>
+__global__ void __launch_bounds__(128) moe_pick_kernel(const float* __restrict__ z, long z_ld, const TW* __restrict__ bias,
+                                                       int* __restrict__ chosen, float* __restrict__ weights, int n_tokens,
+                                                       int experts, int top, int softmax_scores, int renormalise) {
     pdl_wait();
     pdl_trigger();
-    extern __shared__ float route_s[];                  // [experts] scores, [experts] scores + bias
-    float* score = route_s;
-    float* pick = route_s + experts;
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const T* x = h + (long)t * h_ld;
-    for (int e = warp; e < experts; e += 4) {
-        const TW* wr = w_router + (long)e * width;
-        float z = 0.0f;
-        for (int i = lane; i < width; i += 32) z += to_f32<T>(x[i]) * to_f32<TW>(wr[i]);
-        z = warp_sum(z);
-        if (lane == 0) score[e] = z;
-    }
-    __syncthreads();
-    if (warp != 0) return;
+    extern __shared__ float route_s[];                  // per warp: [experts] scores, [experts] scores + bias
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= n_tokens) return;
+    float* score = route_s + (long)warp * 2 * experts;
+    float* pick = score + experts;
+    const float* zr = z + (long)t * z_ld;
     if (softmax_scores) {
         float mx = -CUDART_INF_F;
-        for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, score[e]);
+        for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, zr[e]);
         mx = warp_max(mx);
         float sum = 0.0f;
-        for (int e = lane; e < experts; e += 32) sum += expf(score[e] - mx);
+        for (int e = lane; e < experts; e += 32) sum += expf(zr[e] - mx);
         sum = warp_sum(sum);
-        for (int e = lane; e < experts; e += 32) score[e] = expf(score[e] - mx) / sum;
+        for (int e = lane; e < experts; e += 32) score[e] = expf(zr[e] - mx) / sum;
     } else {
-        for (int e = lane; e < experts; e += 32) score[e] = 1.0f / (1.0f + expf(-score[e]));
+        for (int e = lane; e < experts; e += 32) score[e] = 1.0f / (1.0f + expf(-zr[e]));
     }
     for (int e = lane; e < experts; e += 32) pick[e] = score[e] + (bias ? to_f32<TW>(bias[e]) : 0.0f);
     __syncwarp();
@@ -125,15 +118,13 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const float* __restrict__
     if (lane == 0) out[(long)t * out_ld + c] = from_f32<T>(sum);
 }
 
-FL_API int fl_moe_route(const void* h, int dtype, long h_ld, const void* w_router, const void* bias, int w_dtype,
-                        int* chosen, float* weights, int n_tokens, int width, int experts, int top, int softmax_scores,
-                        int renormalise, cudaStream_t stream) {
+FL_API int fl_moe_pick(const float* z, long z_ld, const void* bias, int bias_dtype, int* chosen, float* weights,
+                       int n_tokens, int experts, int top, int softmax_scores, int renormalise, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (top < 1 || top > experts || (size_t)experts * 8 > 48 * 1024) return (int)cudaErrorInvalidValue;
-    FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
-        return fl_launch(moe_route_kernel<T, TW>, dim3(n_tokens), dim3(128), (size_t)experts * 2 * sizeof(float), stream,
-                         (const T*)h, h_ld, (const TW*)w_router, (const TW*)bias, chosen, weights, width, experts, top,
-                         softmax_scores, renormalise)));
+    if (top < 1 || top > experts || (size_t)experts * 8 * 4 > 48 * 1024) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(bias_dtype, TW,
+        return fl_launch(moe_pick_kernel<TW>, dim3((n_tokens + 3) / 4), dim3(128), (size_t)experts * 8 * sizeof(float), stream,
+                         z, z_ld, (const TW*)bias, chosen, weights, n_tokens, experts, top, softmax_scores, renormalise));
     return 0;
 }
 

@@ -318,33 +318,54 @@ def delta_gated_norm(work, o_col, proj, gate_col, weight, out, heads, vdim, eps)
 
 def latent_prep(proj, q_out, heads, dim, rot, rank, norm_w, eps, cos, sin, positions, slots, cache):
     """The queries' rotated parts, turned, go to the last `rot` columns of each head's block of `q_out`
-    (float32 [N, heads * (rank + rot)]); with `cache` ([pages, page_size, rank + rot]), each token's latent
+    ([N, heads * (rank + rot)], float32 or bfloat16); with `cache` ([pages, page_size, rank + rot]), each token's latent
     is normed and written with the rotated key part into the token's row."""
     _require_cuda(proj, q_out, norm_w, cos, sin, positions, slots, cache)
     if cache is not None and (cache.dtype != proj.dtype or not cache.is_contiguous()):
         raise KernelError("latent_prep: the cache must be contiguous and of the activations' dtype")
-    if q_out.dtype != torch.float32:
-        raise KernelError("latent_prep: q_out must be float32")
-    fn = _fn("latent_attention", "fl_latent_prep", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int,
+    fn = _fn("latent_attention", "fl_latent_prep", [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_int, c_int, c_int, c_int,
                                                     c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
                                                     c_void_p, c_void_p, c_int, c_void_p])
-    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(q_out), _ld(q_out), proj.shape[0], heads, dim, rot, rank,
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(q_out), dtype_code(q_out), _ld(q_out), proj.shape[0], heads,
+              dim, rot, rank,
               _ptr(norm_w), F32 if norm_w is None else dtype_code(norm_w), float(eps), _ptr(cos), _ptr(sin),
               _ptr(positions), _ptr(slots), _ptr(cache), 0 if cache is None else 1, _stream()), "latent_prep")
 
 
 def latent_attention(q, out, cache, block_table, tok_req, positions, heads, rank, rot, window, scale, page_size):
-    """Attention of every token over its request's cache rows; q [N, heads * (rank + rot)] and
-    out [N, heads * rank] float32."""
+    """Attention of every token over its request's cache rows; q [N, heads * (rank + rot)] (float32 or
+    bfloat16) and out [N, heads * rank] float32.  CUDA cores, any sizes, both number formats."""
     _require_cuda(q, out, cache, block_table, tok_req, positions)
-    if q.dtype != torch.float32 or out.dtype != torch.float32:
-        raise KernelError("latent_attention: q and out must be float32")
-    fn = _fn("latent_attention", "fl_latent_attention", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int,
+    if out.dtype != torch.float32:
+        raise KernelError("latent_attention: out must be float32")
+    fn = _fn("latent_attention", "fl_latent_attention", [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_int, c_int,
                                                          c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                          c_int, c_float, c_void_p])
-    _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), dtype_code(cache), page_size, _ptr(block_table),
-              block_table.stride(0), _ptr(tok_req), _ptr(positions), q.shape[0], heads, rank, rot, int(window or 0),
-              float(scale), _stream()), "latent_attention")
+    _check(fn(_ptr(q), dtype_code(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), dtype_code(cache), page_size,
+              _ptr(block_table), block_table.stride(0), _ptr(tok_req), _ptr(positions), q.shape[0], heads, rank, rot,
+              int(window or 0), float(scale), _stream()), "latent_attention")
+
+
+def latent_tc_takes(dtype, rank: int, rot: int) -> bool:
+    """Whether the tensor-core latent attention serves this number format and these sizes."""
+    return dtype == torch.bfloat16 and rank % 32 == 0 and (rank + rot) % 16 == 0 and rank <= 1024
+
+
+def latent_tc_library(rank: int, rot: int):
+    return "latent_attention_tc", {"LAT_RANK": rank, "LAT_ROT": rot}
+
+
+def latent_attention_tc(q, out, cache, block_table, tok_req, positions, heads, rank, rot, window, scale, page_size):
+    """The same on tensor cores: q and cache bfloat16, out float32; one build per (rank, rot)."""
+    _require_cuda(q, out, cache, block_table, tok_req, positions)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.float32:
+        raise KernelError("latent_attention_tc: q and cache bfloat16, out float32")
+    name, defines = latent_tc_library(rank, rot)
+    fn = _fn(name, "fl_latent_attention_tc", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_void_p, c_int,
+                                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p], defines)
+    _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), page_size, _ptr(block_table), block_table.stride(0),
+              _ptr(tok_req), _ptr(positions), q.shape[0], heads, int(window or 0), float(scale), _stream()),
+           "latent_attention_tc")
 
 
 def gemm_simt_batched(a, a_batch, w, out, out_batch):
@@ -362,16 +383,17 @@ def gemm_simt_batched(a, a_batch, w, out, out_batch):
 
 # ------------------------------------------------------------- routed experts
 
-def moe_route(h, w_router, bias, chosen, weights, top, softmax_scores=False, renormalise=False):
-    """Per token the `top` experts by score + bias (int32 `chosen` [N, top]) and their scores (`weights`)."""
-    _require_cuda(h, w_router, bias, chosen, weights)
-    if bias is not None and bias.dtype != w_router.dtype:
-        raise KernelError("moe_route: router matrix and bias must be stored in one dtype")
-    fn = _fn("moe", "fl_moe_route", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                                     c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_ptr(h), dtype_code(h), _ld(h), _ptr(w_router), _ptr(bias), dtype_code(w_router), _ptr(chosen),
-              _ptr(weights), h.shape[0], h.shape[1], w_router.shape[0], top, int(softmax_scores), int(renormalise),
-              _stream()), "moe_route")
+def moe_pick(logits, bias, chosen, weights, top, softmax_scores=False, renormalise=False):
+    """Per token, from the router's float32 logits [N, experts]: the `top` experts by score + bias (int32
+    `chosen` [N, top]) and their scores (`weights`); scores are sigmoids, or a softmax over the experts."""
+    _require_cuda(logits, bias, chosen, weights)
+    if logits.dtype != torch.float32 or chosen.shape[1] != top or not chosen.is_contiguous() or not weights.is_contiguous():
+        raise KernelError("moe_pick: logits float32, chosen and weights contiguous [N, top]")
+    fn = _fn("moe", "fl_moe_pick", [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                    c_int, c_void_p])
+    _check(fn(_ptr(logits), _ld(logits), _ptr(bias), F32 if bias is None else dtype_code(bias), _ptr(chosen),
+              _ptr(weights), logits.shape[0], logits.shape[1], top, int(softmax_scores), int(renormalise), _stream()),
+           "moe_pick")
 
 
 def moe_experts(h, w_gate_up, w_down, chosen, weights, act_buf, out, activation="silu"):

@@ -53,8 +53,6 @@ class GatedDelta(Part):
         self.qk_cols = self.kv_heads * self.dim
         self.hv = self.heads * self.vdim
         self.channels = 2 * self.qk_cols + self.hv                     # what passes the convolution: q | k | v
-        if self.channels * 4 > 48 * 1024:
-            raise ValueError(f"gated_delta: {self.channels} convolved channels exceed the kernel's 12288")
         self.proj_cols = self.channels + self.hv + 2 * self.heads      # ... | gate | b | a
         self.work_cols = 2 * self.qk_cols + self.hv + 2 * self.heads + self.hv   # q | k | v | beta | decay | o
         self.state_floats = self.heads * self.vdim * self.dim

@@ -89,6 +89,9 @@ class LatentAttention(Part):
         for lin in (self.proj, self.o):
             if lin is not None:
                 lin.reserve(self.ctx.dtype, limits.max_tokens)
+        if self.ctx.device.type == "cuda" and ops.latent_tc_takes(self.ctx.dtype, self.rank, self.rot):
+            from ..native.build import load_library
+            load_library(*ops.latent_tc_library(self.rank, self.rot))      # built now, not inside the first step
 
     def forward(self, h, out, step, cache):
         n = h.shape[0]
@@ -99,14 +102,16 @@ class LatentAttention(Part):
         cols = self.q_cols if self.shares_cache else self.q_cols + self.width
         proj = ws.rows("latent_proj", n, cols, dt)
         self.proj.forward(h, proj)
-        q = ws.rows("latent_q", n, self.heads * self.width, torch.float32)
+        tc = ops.latent_tc_takes(dt, self.rank, self.rot)     # bfloat16 and sizes the tensor-core kernel is built for
+        q = ws.rows("latent_q", n, self.heads * self.width, dt if tc else torch.float32)
         cos, sin = self.position.tables()
         ops.latent_prep(proj, q, self.heads, self.dim, self.rot, self.rank, self.dkv_norm, self.norm_eps, cos, sin,
                         step.positions, cache.slots, cache.tensor if cache.writes else None)
         ops.gemm_simt_batched(proj, self.dim + self.rot, self.uk_t, q, self.width)
         mix = ws.rows("latent_mix", n, self.heads * self.rank, torch.float32)
-        ops.latent_attention(q, mix, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
-                             self.rank, self.rot, self.window, self.scale, cache.page_size)
+        attend = ops.latent_attention_tc if tc else ops.latent_attention
+        attend(q, mix, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
+               self.rank, self.rot, self.window, self.scale, cache.page_size)
         ctx = ws.rows("latent_ctx", n, self.heads * self.vdim, dt)
         ops.gemm_simt_batched(mix, self.rank, self.uv, ctx, self.vdim)
         return self.o.forward(ctx, out, defer=True)

@@ -22,6 +22,7 @@ import torch
 
 from ..native import ops, scratch
 from .base import Part
+from .linear import Linear
 from .registry import register_part
 
 
@@ -64,7 +65,7 @@ class RoutedExperts(Part):
         return shapes
 
     def load(self, tensors):
-        self.router = tensors["router"].contiguous()
+        self.router = Linear([tensors["router"]])
         self.correction = tensors["correction"].contiguous() if self.choice_bias else None
         first = tensors["gate.0"]
         self.gate_up = torch.empty((self.experts, 2 * self.ff, self.hidden), dtype=first.dtype, device=first.device)
@@ -89,6 +90,7 @@ class RoutedExperts(Part):
         return ints, act, y
 
     def reserve(self, limits):
+        self.router.reserve(self.ctx.dtype, limits.max_tokens)
         if self.ctx.device.type == "cuda" and self._grouped(self.ctx.dtype):
             self._group_buffers(limits.max_tokens, self.ctx.device)       # sized now: nothing grows under a graph
 
@@ -97,8 +99,9 @@ class RoutedExperts(Part):
         ws = step.workspace
         chosen = ws.rows("moe_chosen", n, self.top, torch.int32)
         weights = ws.rows("moe_weights", n, self.top, torch.float32)
-        ops.moe_route(h, self.router, self.correction, chosen, weights, self.top, self.score == "softmax",
-                      self.renormalise)
+        logits = ws.rows("moe_logits", n, self.experts, torch.float32)
+        self.router.forward(h, logits)                       # float accumulation, float logits
+        ops.moe_pick(logits, self.correction, chosen, weights, self.top, self.score == "softmax", self.renormalise)
         if n * self.top >= self.GROUP_FROM and self._grouped(h.dtype):
             ints, act, y = self._group_buffers(n, h.device)
             ops.moe_experts_grouped(h, self.gate_up, self.down, chosen, weights, ints, act, y, out, self.activation)

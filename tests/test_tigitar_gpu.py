@@ -291,17 +291,47 @@ def test_router_kernel_choice_weights_and_ties():
     bias = torch.randn(9, device="cuda")
     chosen = torch.empty(50, 4, dtype=torch.int32, device="cuda")
     weights = torch.empty(50, 4, device="cuda")
-    ops.moe_route(h, wr, bias, chosen, weights, 4)
-    s = torch.sigmoid(h.double() @ wr.double().T)
+    z = (h.double() @ wr.double().T).float()
+    ops.moe_pick(z, bias, chosen, weights, 4)
+    s = torch.sigmoid(z.double())
     ref = torch.topk(s + bias.double(), 4, dim=-1).indices
     assert torch.equal(chosen.long().sort(-1).values, ref.sort(-1).values)
     assert float((weights.double() - s.gather(1, chosen.long())).abs().max()) <= 1e-6
     chosen3 = torch.empty(50, 3, dtype=torch.int32, device="cuda")
     weights3 = torch.empty(50, 3, device="cuda")
-    ops.moe_route(h, wr, None, chosen3, weights3, 3, True, True)      # softmax scores, renormalised
-    p = torch.softmax(h.double() @ wr.double().T, -1)
+    ops.moe_pick(z, None, chosen3, weights3, 3, True, True)           # softmax scores, renormalised
+    p = torch.softmax(z.double(), -1)
     top = torch.topk(p, 3, dim=-1)
     assert torch.equal(chosen3.long(), top.indices)
     assert float((weights3.double() - top.values / top.values.sum(-1, keepdim=True)).abs().max()) <= 1e-6
-    ops.moe_route(torch.zeros(2, 24, device="cuda"), wr, None, chosen[:2], weights[:2], 4)   # all scores equal
-    assert chosen[:2].tolist() == [[0, 1, 2, 3]] * 2
+    two, two_w = torch.empty(2, 4, dtype=torch.int32, device="cuda"), torch.empty(2, 4, device="cuda")
+    ops.moe_pick(torch.zeros(2, 9, device="cuda"), None, two, two_w, 4)                      # all scores equal
+    assert two.tolist() == [[0, 1, 2, 3]] * 2
+
+
+@pytest.mark.parametrize("rank,rot,heads,window", [(96, 16, 4, 37), (64, 16, 19, None), (256, 32, 16, 100)])
+def test_tensor_core_latent_attention_against_the_cuda_core_kernel(rank, rot, heads, window):
+    """Scattered pages, prompt portions beside single tokens, windows that end inside a tile of keys; one
+    query and key scaled so that a single far key just inside the window carries its row."""
+    from fastllm_py_b200.native import ops
+
+    torch.manual_seed(rank)
+    page, width, n_pages = 8, rank + rot, 64
+    cache = torch.randn(n_pages, page, width, device="cuda").to(torch.bfloat16)
+    lens = [(0, 70), (150, 1), (33, 9), (199, 1)]                     # (cached before the step, tokens in it)
+    table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(len(lens), -1).contiguous()
+    tok_req = torch.tensor([r for r, (_, n) in enumerate(lens) for _ in range(n)], dtype=torch.int32, device="cuda")
+    positions = torch.tensor([c + i for c, n in lens for i in range(n)], dtype=torch.int32, device="cuda")
+    n = tok_req.numel()
+    q = (0.3 * torch.randn(n, heads * width, device="cuda")).to(torch.bfloat16)
+    if window is not None:                                                # request 1's token sees position 150 - window + 1 last
+        far = 150 - window + 1
+        row = cache[table[1, far // page].long(), far % page]
+        q[70, :width] = (4.0 * row.float() / row.float().norm()).to(torch.bfloat16)
+    want = torch.empty(n, heads * rank, device="cuda")
+    got = torch.empty_like(want)
+    ops.latent_attention(q, want, cache, table, tok_req, positions, heads, rank, rot, window, 0.2, page)
+    ops.latent_attention_tc(q, got, cache, table, tok_req, positions, heads, rank, rot, window, 0.2, page)
+    torch.cuda.synchronize()
+    assert float((got - want).abs().max()) <= 2e-2
+    assert float((got - want).abs().mean()) <= 2e-3
