@@ -11,7 +11,8 @@
 //                     the portion's start, from the request's saved tail), silu, unit norms, beta, decay
 //   delta_tail        per request: the last taps - 1 raw inputs of the portion become the saved tail
 //   delta_scan        per (request, head, 32 value columns): the recurrence over the portion's tokens,
-//                     one value column's state spread over eight lanes' registers
+//                     one value column's state spread over eight lanes' registers, inputs staged
+//                     through shared memory a chunk of tokens ahead
 //   delta_gated_norm  per (token, head): o / rms(o) * w * silu(gate)
 //
 // A request's state row is [heads][vdim][dim] floats (a column of S is contiguous) followed by the
@@ -102,7 +103,16 @@ __global__ void delta_tail_kernel(const T* __restrict__ proj, long ld, float* __
 }
 
 // One block: one request, one head, DELTA_COLS value columns.  Thread (col, part) keeps the elements
-// d = i * DELTA_PARTS + part of column `col` of S.
+// d = i * DELTA_PARTS + part of column `col` of S.  The tokens' inputs (k, q of the head, the block's v
+// columns, beta, decay) come through shared memory in chunks of DELTA_CHUNK tokens, the next chunk in
+// flight (cp.async) while this one is consumed: the recurrence itself never waits for global memory.
+#define DELTA_CHUNK 16
+
+__device__ __forceinline__ void delta_cp4(float* smem, const float* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem));
+}
+
 template <int DPT>
 __global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
     float* __restrict__ work, long work_ld, float* __restrict__ state, long state_stride,
@@ -110,6 +120,7 @@ __global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
     const int* __restrict__ req_slot, int heads, int kv_heads, int dim, int vdim) {
     pdl_wait();
     pdl_trigger();
+    extern __shared__ float delta_in[];                      // [2][DELTA_CHUNK][k dim | q dim | v DELTA_COLS | beta | decay]
     const int r = blockIdx.x / heads, h = blockIdx.x % heads;
     const int g = h / (heads / kv_heads);
     const int part = threadIdx.x & (DELTA_PARTS - 1), col = threadIdx.x / DELTA_PARTS;
@@ -119,50 +130,66 @@ __global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
     const int start = req_start[r], qlen = req_qlen[r];
     float* s_col = state + (long)req_slot[r] * state_stride + ((long)h * vdim + jj) * dim;
     const int qk_cols = kv_heads * dim, hv = heads * vdim;
-    float S[DPT], k[DPT], q[DPT], k_next[DPT], q_next[DPT];
+    const int per_token = 2 * dim + DELTA_COLS + 2;
+    const int v0 = blockIdx.y * DELTA_COLS;
+    auto fetch = [&](int buf, int first) {                   // tokens first .. first + DELTA_CHUNK - 1 of the portion
+        float* dst = delta_in + (long)buf * DELTA_CHUNK * per_token;
+        const int n_tok = min(DELTA_CHUNK, qlen - first);
+        for (int idx = threadIdx.x; idx < n_tok * per_token; idx += blockDim.x) {
+            const int n = idx / per_token, e = idx % per_token;
+            const float* row = work + (long)(start + first + n) * work_ld;
+            const float* src;
+            if (e < dim) src = row + qk_cols + g * dim + e;                       // k
+            else if (e < 2 * dim) src = row + g * dim + (e - dim);                // q
+            else if (e < 2 * dim + DELTA_COLS) src = row + 2 * qk_cols + h * vdim + min(v0 + e - 2 * dim, vdim - 1);
+            else src = row + 2 * qk_cols + hv + (e - 2 * dim - DELTA_COLS) * heads + h;   // beta, decay
+            delta_cp4(dst + idx, src);
+        }
+        asm volatile("cp.async.commit_group;");
+    };
+    float S[DPT];
     const bool fresh = req_ctx[r] == 0;
+    fetch(0, 0);
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = i * DELTA_PARTS + part;
         S[i] = (!fresh && d < dim) ? s_col[d] : 0.0f;
-        k_next[i] = q_next[i] = 0.0f;
     }
-    // the next token's inputs are asked for before this token's arithmetic: they do not depend on S
-    auto fetch = [&](int t, float* kk, float* qq, float& v, float& beta, float& decay) {
-        const float* row = work + (long)t * work_ld;
-        const float* qrow = row + g * dim;
-#pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-            const int d = i * DELTA_PARTS + part;
-            kk[i] = d < dim ? qrow[qk_cols + d] : 0.0f;
-            qq[i] = d < dim ? qrow[d] : 0.0f;
+    float* o_base = work + (long)start * work_ld + 2 * qk_cols + hv + 2 * heads + h * vdim + j;
+    for (int first = 0, buf = 0; first < qlen; first += DELTA_CHUNK, buf ^= 1) {
+        if (first + DELTA_CHUNK < qlen) {
+            fetch(buf ^ 1, first + DELTA_CHUNK);
+            asm volatile("cp.async.wait_group 1;");
+        } else {
+            asm volatile("cp.async.wait_group 0;");
         }
-        v = row[2 * qk_cols + h * vdim + jj];
-        beta = row[2 * qk_cols + hv + h];
-        decay = row[2 * qk_cols + hv + heads + h];
-    };
-    float v, beta, decay, v_next = 0.0f, beta_next = 0.0f, decay_next = 0.0f;
-    fetch(start, k, q, v, beta, decay);
-    for (int n = 0; n < qlen; ++n) {
-        if (n + 1 < qlen) fetch(start + n + 1, k_next, q_next, v_next, beta_next, decay_next);
-        float dot = 0.0f;
+        __syncthreads();
+        const float* in = delta_in + (long)buf * DELTA_CHUNK * per_token;
+        const int n_tok = min(DELTA_CHUNK, qlen - first);
+        for (int n = 0; n < n_tok; ++n, in += per_token) {
+            float k[DPT], dot = 0.0f;
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) dot += S[i] * k[i];
+            for (int i = 0; i < DPT; ++i) {
+                const int d = i * DELTA_PARTS + part;
+                k[i] = d < dim ? in[d] : 0.0f;
+                dot += S[i] * k[i];
+            }
 #pragma unroll
-        for (int o = 1; o < DELTA_PARTS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        const float u = beta * (v - decay * dot);
-        float out = 0.0f;
+            for (int o = 1; o < DELTA_PARTS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const float decay = in[2 * dim + DELTA_COLS + 1];
+            const float u = in[2 * dim + DELTA_COLS] * (in[2 * dim + col] - decay * dot);
+            float out = 0.0f;
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) {
-            S[i] = decay * S[i] + k[i] * u;
-            out += S[i] * q[i];
+            for (int i = 0; i < DPT; ++i) {
+                const int d = i * DELTA_PARTS + part;
+                S[i] = decay * S[i] + k[i] * u;
+                out += S[i] * (d < dim ? in[dim + d] : 0.0f);
+            }
+#pragma unroll
+            for (int o = 1; o < DELTA_PARTS; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+            if (live && part == 0) o_base[(long)(first + n) * work_ld] = out;
         }
-#pragma unroll
-        for (int o = 1; o < DELTA_PARTS; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-        if (live && part == 0) work[(long)(start + n) * work_ld + 2 * qk_cols + hv + 2 * heads + h * vdim + j] = out;
-#pragma unroll
-        for (int i = 0; i < DPT; ++i) { k[i] = k_next[i]; q[i] = q_next[i]; }
-        v = v_next; beta = beta_next; decay = decay_next;
+        __syncthreads();                                     // the chunk is overwritten by the fetch after next
     }
     if (live) {
 #pragma unroll
@@ -230,11 +257,12 @@ FL_API int fl_delta_scan(float* work, long work_ld, float* state, long state_str
     if (n_requests <= 0) return 0;
     if (heads % kv_heads || dim < 1 || dim > 32 * DELTA_PARTS) return (int)cudaErrorInvalidValue;
     const int per_thread = (dim + DELTA_PARTS - 1) / DELTA_PARTS;
+    const size_t smem = (size_t)2 * DELTA_CHUNK * (2 * dim + DELTA_COLS + 2) * sizeof(float);     // <= 35 KB
     dim3 grid(n_requests * heads, (vdim + DELTA_COLS - 1) / DELTA_COLS);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
 #define FL_DELTA_SCAN(DPT)                                                                                          \
     if (per_thread <= DPT)                                                                                          \
-        return fl_launch(delta_scan_kernel<DPT>, grid, dim3(DELTA_COLS * DELTA_PARTS), 0, stream, work, work_ld, state, \
+        return fl_launch(delta_scan_kernel<DPT>, grid, dim3(DELTA_COLS * DELTA_PARTS), smem, stream, work, work_ld, state, \
                          state_stride, req_start, req_ctx, req_qlen, req_slot, heads, kv_heads, dim, vdim)
     FL_DELTA_SCAN(2);
     FL_DELTA_SCAN(4);

@@ -34,7 +34,7 @@ __device__ __forceinline__ void lt_cp16(void* smem, const void* gmem, int bytes)
 __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
     const bf16* __restrict__ q, long q_ld, float* __restrict__ out, long out_ld, const bf16* __restrict__ cache,
     int page_size, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
-    const int* __restrict__ positions, int heads, int window, float scale) {
+    const int* __restrict__ positions, int heads, int window, float scale, int split_keys, float* __restrict__ partial) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ __align__(16) unsigned char lt_smem[];
@@ -62,7 +62,27 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
         }
         asm volatile("cp.async.commit_group;");
     };
-    const int first_tile = (lo / LT_KEYS) * LT_KEYS;
+    // with split_keys (a multiple of LT_KEYS) the block takes only the keys of split blockIdx.z, counted from
+    // the multiple of split_keys at or below the first visible key, and leaves (accumulator, maximum, sum)
+    // in `partial` for the merge kernel; the splits' borders depend on the token's own position only
+    int first_tile = (lo / LT_KEYS) * LT_KEYS, last = pos;
+    if (split_keys > 0) {
+        first_tile = (lo / split_keys + (int)blockIdx.z) * split_keys;
+        last = min(pos, first_tile + split_keys - 1);
+        first_tile = max(first_tile, (lo / LT_KEYS) * LT_KEYS);      // (no tile wholly out of sight: its maximum would be -inf)
+    }
+    float* part_row = nullptr;
+    if (split_keys > 0) {
+        part_row = partial + (((long)t * heads) * gridDim.z + blockIdx.z) * (LAT_RANK + 2);     // + head * gridDim.z * (rank + 2)
+        if (first_tile > pos) {                              // nothing of this split is in sight
+            for (int r = tid; r < 16 && head0 + r < heads; r += LT_WARPS * 32) {
+                float* pr = part_row + (long)(head0 + r) * gridDim.z * (LAT_RANK + 2);
+                pr[LAT_RANK] = -CUDART_INF_F;
+                pr[LAT_RANK + 1] = 0.0f;
+            }
+            return;
+        }
+    }
     stage(0, first_tile);
     for (int c = tid; c < 16 * (LT_WIDTH / 8); c += LT_WARPS * 32) {     // the 16 heads' q~
         const int r = c / (LT_WIDTH / 8), piece = c % (LT_WIDTH / 8);
@@ -76,8 +96,8 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
     float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.0f, 0.0f};   // rows lane / 4 and lane / 4 + 8
     const int row0 = lane >> 2;
     int buf = 0;
-    for (int tile = first_tile; tile <= pos; tile += LT_KEYS, buf ^= 1) {
-        if (tile + LT_KEYS <= pos) {
+    for (int tile = first_tile; tile <= last; tile += LT_KEYS, buf ^= 1) {
+        if (tile + LT_KEYS <= last) {
             stage(buf ^ 1, tile + LT_KEYS);
             asm volatile("cp.async.wait_group 1;");
         } else {
@@ -165,6 +185,25 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
         }
         __syncthreads();                                     // the tile, p_s and the reductions are rewritten next
     }
+    if (split_keys > 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int head = head0 + row0 + h * 8;
+            if (head >= heads) continue;
+            float* pr = part_row + (long)head * gridDim.z * (LAT_RANK + 2);
+            float* o = pr + warp * LT_VCOLS + (lane & 3) * 2;
+#pragma unroll
+            for (int n = 0; n < LT_NT; ++n) {
+                o[n * 8] = acc[n][h * 2];
+                o[n * 8 + 1] = acc[n][h * 2 + 1];
+            }
+            if (warp == 0 && (lane & 3) == 0) {
+                pr[LAT_RANK] = m_run[h];
+                pr[LAT_RANK + 1] = l_run[h];
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int head = head0 + row0 + h * 8;
@@ -179,15 +218,46 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
     }
 }
 
+// out[t, head] = sum_z acc_z e^(m_z - M) / sum_z l_z e^(m_z - M), splits in order; one block per (token, head).
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                           long out_ld, int heads, int n_splits) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, head = blockIdx.y;
+    const float* pr = partial + ((long)t * heads + head) * n_splits * (LAT_RANK + 2);
+    float mx = -CUDART_INF_F;
+    for (int z = 0; z < n_splits; ++z) mx = fmaxf(mx, pr[(long)z * (LAT_RANK + 2) + LAT_RANK]);
+    float l = 0.0f;
+    for (int z = 0; z < n_splits; ++z) {
+        const float* p = pr + (long)z * (LAT_RANK + 2);
+        if (p[LAT_RANK + 1] > 0.0f) l += p[LAT_RANK + 1] * expf(p[LAT_RANK] - mx);
+    }
+    for (int c = threadIdx.x; c < LAT_RANK; c += blockDim.x) {
+        float sum = 0.0f;
+        for (int z = 0; z < n_splits; ++z) {
+            const float* p = pr + (long)z * (LAT_RANK + 2);
+            if (p[LAT_RANK + 1] > 0.0f) sum += p[c] * expf(p[LAT_RANK] - mx);
+        }
+        out[(long)t * out_ld + (long)head * LAT_RANK + c] = sum / l;
+    }
+}
+
 FL_API int fl_latent_attention_tc_rank() { return LAT_RANK; }
 FL_API int fl_latent_attention_tc_rot() { return LAT_ROT; }
 
 // q: bfloat16 [n_tokens, heads x (rank + rot)], rows 16-byte aligned; out: float [n_tokens, heads x rank];
 // cache: bfloat16 [pages][page_size][rank + rot].  window <= 0: all earlier tokens.
+// split_keys > 0 (a multiple of 32): the keys are shared out over n_splits blocks per token (decode steps,
+// where tokens are too few to fill the GPU); `partial` then holds n_tokens * heads * n_splits * (rank + 2)
+// floats and a merge kernel follows.  n_splits must reach the last key of every token:
+// (longest visible span - 1) / split_keys + 2 does.
 FL_API int fl_latent_attention_tc(const void* q, long q_ld, float* out, long out_ld, const void* cache, int page_size,
                                   const int* block_table, int bt_stride, const int* tok_req, const int* positions,
-                                  int n_tokens, int heads, int window, float scale, cudaStream_t stream) {
+                                  int n_tokens, int heads, int window, float scale, int split_keys, int n_splits,
+                                  float* partial, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (split_keys < 0 || split_keys % LT_KEYS || (split_keys > 0 && (n_splits < 1 || n_splits > 65535 || partial == nullptr)))
+        return (int)cudaErrorInvalidValue;
     if (((uintptr_t)q % 16) || (q_ld % 8) || ((uintptr_t)cache % 16) || (heads + 15) / 16 > 65535)
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(16 * LT_PITCH + 2 * LT_KEYS * LT_PITCH + 16 * LT_PPITCH) * sizeof(bf16) +
@@ -198,7 +268,11 @@ FL_API int fl_latent_attention_tc(const void* q, long q_ld, float* out, long out
         if (rc != cudaSuccess) return (int)rc;
         raised = true;
     }
-    return fl_launch(latent_attention_tc_kernel, dim3(n_tokens, (heads + 15) / 16), dim3(LT_WARPS * 32), smem, stream,
-                     (const bf16*)q, q_ld, out, out_ld, (const bf16*)cache, page_size, block_table, bt_stride, tok_req,
-                     positions, heads, window, scale);
+    const int rc = fl_launch(latent_attention_tc_kernel, dim3(n_tokens, (heads + 15) / 16, split_keys > 0 ? n_splits : 1),
+                             dim3(LT_WARPS * 32), smem, stream, (const bf16*)q, q_ld, out, out_ld, (const bf16*)cache,
+                             page_size, block_table, bt_stride, tok_req, positions, heads, window, scale, split_keys,
+                             partial);
+    if (rc || split_keys == 0) return rc;
+    return fl_launch(latent_merge_kernel, dim3(n_tokens, heads), dim3(128), 0, stream, (const float*)partial, out, out_ld,
+                     heads, n_splits);
 }

@@ -355,17 +355,24 @@ def latent_tc_library(rank: int, rot: int):
     return "latent_attention_tc", {"LAT_RANK": rank, "LAT_ROT": rot}
 
 
-def latent_attention_tc(q, out, cache, block_table, tok_req, positions, heads, rank, rot, window, scale, page_size):
-    """The same on tensor cores: q and cache bfloat16, out float32; one build per (rank, rot)."""
+def latent_attention_tc(q, out, cache, block_table, tok_req, positions, heads, rank, rot, window, scale, page_size,
+                        split_keys=0, n_splits=1, partial=None):
+    """The same on tensor cores: q and cache bfloat16, out float32; one build per (rank, rot).  With
+    `split_keys` (a multiple of 32) each token's keys are shared out over `n_splits` blocks, which must reach
+    every token's last key ((longest visible span - 1) // split_keys + 2 does), and merged from `partial`
+    (float32, N * heads * n_splits * (rank + 2))."""
     _require_cuda(q, out, cache, block_table, tok_req, positions)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.float32:
         raise KernelError("latent_attention_tc: q and cache bfloat16, out float32")
     name, defines = latent_tc_library(rank, rot)
+    if split_keys and (partial is None or partial.numel() < q.shape[0] * heads * n_splits * (rank + 2)):
+        raise KernelError("latent_attention_tc: the buffer for the splits' results is too small")
     fn = _fn(name, "fl_latent_attention_tc", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_void_p, c_int,
-                                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p], defines)
+                                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                              c_void_p], defines)
     _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), page_size, _ptr(block_table), block_table.stride(0),
-              _ptr(tok_req), _ptr(positions), q.shape[0], heads, int(window or 0), float(scale), _stream()),
-           "latent_attention_tc")
+              _ptr(tok_req), _ptr(positions), q.shape[0], heads, int(window or 0), float(scale), int(split_keys),
+              int(n_splits), _ptr(partial), _stream()), "latent_attention_tc", 2 if split_keys else 1)
 
 
 def gemm_simt_batched(a, a_batch, w, out, out_batch):

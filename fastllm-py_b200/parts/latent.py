@@ -24,7 +24,7 @@ from __future__ import annotations
 import torch
 
 from ..cache.needs import PagedRows
-from ..native import ops
+from ..native import ops, scratch
 from .base import Part
 from .linear import Linear
 from .registry import build_part, register_part
@@ -38,6 +38,8 @@ class LatentAttention(Part):
     o [hidden, heads * vdim] and, unless shares_cache, dkv [kv_rank + rot_dim, hidden], dkv_norm [kv_rank]."""
     category = "mixer"
     native_libraries = ("latent_attention",)
+    SPLIT_BELOW = 64                 # blocks (tokens x groups of 16 heads) under which a step's keys are split
+    SCRATCH = "latent attention splits"
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -92,6 +94,35 @@ class LatentAttention(Part):
         if self.ctx.device.type == "cuda" and ops.latent_tc_takes(self.ctx.dtype, self.rank, self.rot):
             from ..native.build import load_library
             load_library(*ops.latent_tc_library(self.rank, self.rot))      # built now, not inside the first step
+            most = max(1, (self.SPLIT_BELOW - 1) // -(-self.heads // 16))   # tokens of the largest step that splits
+            longest = -(-limits.max_model_len // 1024) * 1024
+            self._partials(min(most, limits.max_tokens), self._split(1, longest)[1])   # nothing grows under a graph
+
+    # ---- what the host decides per step: whether and how the tensor-core kernel splits the keys
+    @property
+    def plan_key(self):
+        return ("latent_attention", self.heads, self.rank, self.rot, self.window)
+
+    def _split(self, n_tokens: int, longest: int):
+        """(keys per split, splits) for a step of n_tokens whose longest sequence is `longest`; (0, 1): no split."""
+        if not ops.latent_tc_takes(self.ctx.dtype, self.rank, self.rot) or \
+                n_tokens * -(-self.heads // 16) >= self.SPLIT_BELOW:
+            return 0, 1
+        span = longest if self.window is None else min(self.window, longest)
+        keys = max(128, -(-span // (30 * 32)) * 32)           # at most 32 splits
+        return keys, (span - 1) // keys + 2
+
+    def plan_step(self, step):
+        longest = step.max_seq_len
+        if step.for_graph:                                    # a captured step serves many: cover the length rounded up
+            longest = -(-longest // 1024) * 1024
+        step.plans[self.plan_key] = self._split(step.n_tokens, longest)
+
+    def graph_key(self, step):
+        return step.plans.get(self.plan_key)
+
+    def _partials(self, n_tokens: int, n_splits: int):
+        return scratch.get(self.ctx.device, self.SCRATCH, n_tokens * self.heads * n_splits * (self.rank + 2))
 
     def forward(self, h, out, step, cache):
         n = h.shape[0]
@@ -109,9 +140,16 @@ class LatentAttention(Part):
                         step.positions, cache.slots, cache.tensor if cache.writes else None)
         ops.gemm_simt_batched(proj, self.dim + self.rot, self.uk_t, q, self.width)
         mix = ws.rows("latent_mix", n, self.heads * self.rank, torch.float32)
-        attend = ops.latent_attention_tc if tc else ops.latent_attention
-        attend(q, mix, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
-               self.rank, self.rot, self.window, self.scale, cache.page_size)
+        if tc:
+            if self.plan_key not in step.plans:               # a step built by hand, not by the engine
+                self.plan_step(step)
+            keys, splits = step.plans[self.plan_key]
+            ops.latent_attention_tc(q, mix, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
+                                    self.rank, self.rot, self.window, self.scale, cache.page_size, keys, splits,
+                                    self._partials(n, splits) if keys else None)
+        else:
+            ops.latent_attention(q, mix, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
+                                 self.rank, self.rot, self.window, self.scale, cache.page_size)
         ctx = ws.rows("latent_ctx", n, self.heads * self.vdim, dt)
         ops.gemm_simt_batched(mix, self.rank, self.uv, ctx, self.vdim)
         return self.o.forward(ctx, out, defer=True)

@@ -97,8 +97,10 @@ class RoutedExperts(Part):
     def forward(self, h, out, step):
         n = h.shape[0]
         ws = step.workspace
-        chosen = ws.rows("moe_chosen", n, self.top, torch.int32)
-        weights = ws.rows("moe_weights", n, self.top, torch.float32)
+        # [n, top] without gaps between rows (the workspace pads rows to 16 bytes; whole padded rows are dense)
+        padded = -(-self.top // 4) * 4
+        chosen = ws.rows("moe_chosen", n, padded, torch.int32).view(-1)[:n * self.top].view(n, self.top)
+        weights = ws.rows("moe_weights", n, padded, torch.float32).view(-1)[:n * self.top].view(n, self.top)
         logits = ws.rows("moe_logits", n, self.experts, torch.float32)
         self.router.forward(h, logits)                       # float accumulation, float logits
         ops.moe_pick(logits, self.correction, chosen, weights, self.top, self.score == "softmax", self.renormalise)

@@ -332,6 +332,12 @@ def test_tensor_core_latent_attention_against_the_cuda_core_kernel(rank, rot, he
     got = torch.empty_like(want)
     ops.latent_attention(q, want, cache, table, tok_req, positions, heads, rank, rot, window, 0.2, page)
     ops.latent_attention_tc(q, got, cache, table, tok_req, positions, heads, rank, rot, window, 0.2, page)
+    split = torch.empty_like(want)                                    # the same with the keys shared out over blocks
+    span = 200 if window is None else min(window, 200)
+    parts = torch.empty(n * heads * ((span - 1) // 64 + 2) * (rank + 2), device="cuda")
+    ops.latent_attention_tc(q, split, cache, table, tok_req, positions, heads, rank, rot, window, 0.2, page,
+                            64, (span - 1) // 64 + 2, parts)
     torch.cuda.synchronize()
-    assert float((got - want).abs().max()) <= 2e-2
-    assert float((got - want).abs().mean()) <= 2e-3
+    for result in (got, split):
+        assert float((result - want).abs().max()) <= 2e-2
+        assert float((result - want).abs().mean()) <= 2e-3
