@@ -167,27 +167,32 @@ __global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
         const float* in = delta_in + (long)buf * DELTA_CHUNK * per_token;
         const int n_tok = min(DELTA_CHUNK, qlen - first);
         for (int n = 0; n < n_tok; ++n, in += per_token) {
-            float k[DPT], dot = 0.0f;
+            // With a = S^T k, b = S^T q (S before the token) and c = q . k:  u = beta (v - g a) and the
+            // read-out of the updated state is g b + c u.  The three sums are independent, so their chains
+            // and their reductions over the column's lanes overlap; only u stands between this token's
+            // sums and the next token's.
+            float k[DPT], a[2] = {0.0f, 0.0f}, bq[2] = {0.0f, 0.0f}, c[2] = {0.0f, 0.0f};
 #pragma unroll
             for (int i = 0; i < DPT; ++i) {
                 const int d = i * DELTA_PARTS + part;
                 k[i] = d < dim ? in[d] : 0.0f;
-                dot += S[i] * k[i];
+                const float qv = d < dim ? in[dim + d] : 0.0f;
+                a[i & 1] += S[i] * k[i];
+                bq[i & 1] += S[i] * qv;
+                c[i & 1] += qv * k[i];
             }
+            float dot = a[0] + a[1], read = bq[0] + bq[1], qk = c[0] + c[1];
 #pragma unroll
-            for (int o = 1; o < DELTA_PARTS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            for (int o = 1; o < DELTA_PARTS; o <<= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                read += __shfl_xor_sync(0xffffffffu, read, o);
+                qk += __shfl_xor_sync(0xffffffffu, qk, o);
+            }
             const float decay = in[2 * dim + DELTA_COLS + 1];
             const float u = in[2 * dim + DELTA_COLS] * (in[2 * dim + col] - decay * dot);
-            float out = 0.0f;
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = i * DELTA_PARTS + part;
-                S[i] = decay * S[i] + k[i] * u;
-                out += S[i] * (d < dim ? in[dim + d] : 0.0f);
-            }
-#pragma unroll
-            for (int o = 1; o < DELTA_PARTS; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-            if (live && part == 0) o_base[(long)(first + n) * work_ld] = out;
+            for (int i = 0; i < DPT; ++i) S[i] = fmaf(k[i], u, decay * S[i]);
+            if (live && part == 0) o_base[(long)(first + n) * work_ld] = decay * read + qk * u;
         }
         __syncthreads();                                     // the chunk is overwritten by the fetch after next
     }

@@ -31,8 +31,9 @@ __device__ __forceinline__ void lt_cp16(void* smem, const void* gmem, int bytes)
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes));
 }
 
+template <typename TO>
 __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
-    const bf16* __restrict__ q, long q_ld, float* __restrict__ out, long out_ld, const bf16* __restrict__ cache,
+    const bf16* __restrict__ q, long q_ld, TO* __restrict__ out, long out_ld, const bf16* __restrict__ cache,
     int page_size, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
     const int* __restrict__ positions, int heads, int window, float scale, int split_keys, float* __restrict__ partial) {
     pdl_wait();
@@ -208,18 +209,19 @@ __global__ void __launch_bounds__(LT_WARPS * 32) latent_attention_tc_kernel(
     for (int h = 0; h < 2; ++h) {
         const int head = head0 + row0 + h * 8;
         if (head >= heads) continue;
-        float* o = out + (long)t * out_ld + (long)head * LAT_RANK + warp * LT_VCOLS + (lane & 3) * 2;
+        TO* o = out + (long)t * out_ld + (long)head * LAT_RANK + warp * LT_VCOLS + (lane & 3) * 2;
         const float inv = 1.0f / l_run[h];
 #pragma unroll
         for (int n = 0; n < LT_NT; ++n) {
-            o[n * 8] = acc[n][h * 2] * inv;
-            o[n * 8 + 1] = acc[n][h * 2 + 1] * inv;
+            o[n * 8] = from_f32<TO>(acc[n][h * 2] * inv);
+            o[n * 8 + 1] = from_f32<TO>(acc[n][h * 2 + 1] * inv);
         }
     }
 }
 
 // out[t, head] = sum_z acc_z e^(m_z - M) / sum_z l_z e^(m_z - M), splits in order; one block per (token, head).
-__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ partial, float* __restrict__ out,
+template <typename TO>
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ partial, TO* __restrict__ out,
                                                            long out_ld, int heads, int n_splits) {
     pdl_wait();
     pdl_trigger();
@@ -238,20 +240,20 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
             const float* p = pr + (long)z * (LAT_RANK + 2);
             if (p[LAT_RANK + 1] > 0.0f) sum += p[c] * expf(p[LAT_RANK] - mx);
         }
-        out[(long)t * out_ld + (long)head * LAT_RANK + c] = sum / l;
+        out[(long)t * out_ld + (long)head * LAT_RANK + c] = from_f32<TO>(sum / l);
     }
 }
 
 FL_API int fl_latent_attention_tc_rank() { return LAT_RANK; }
 FL_API int fl_latent_attention_tc_rot() { return LAT_ROT; }
 
-// q: bfloat16 [n_tokens, heads x (rank + rot)], rows 16-byte aligned; out: float [n_tokens, heads x rank];
+// q: bfloat16 [n_tokens, heads x (rank + rot)], rows 16-byte aligned; out: float or bfloat16 [n_tokens, heads x rank];
 // cache: bfloat16 [pages][page_size][rank + rot].  window <= 0: all earlier tokens.
 // split_keys > 0 (a multiple of 32): the keys are shared out over n_splits blocks per token (decode steps,
 // where tokens are too few to fill the GPU); `partial` then holds n_tokens * heads * n_splits * (rank + 2)
 // floats and a merge kernel follows.  n_splits must reach the last key of every token:
 // (longest visible span - 1) / split_keys + 2 does.
-FL_API int fl_latent_attention_tc(const void* q, long q_ld, float* out, long out_ld, const void* cache, int page_size,
+FL_API int fl_latent_attention_tc(const void* q, long q_ld, void* out, int out_dtype, long out_ld, const void* cache, int page_size,
                                   const int* block_table, int bt_stride, const int* tok_req, const int* positions,
                                   int n_tokens, int heads, int window, float scale, int split_keys, int n_splits,
                                   float* partial, cudaStream_t stream) {
@@ -264,15 +266,20 @@ FL_API int fl_latent_attention_tc(const void* q, long q_ld, float* out, long out
                         2 * LT_WARPS * 16 * sizeof(float);
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
-        const cudaError_t rc = cudaFuncSetAttribute(latent_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t rc = cudaFuncSetAttribute(latent_attention_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (rc == cudaSuccess)
+            rc = cudaFuncSetAttribute(latent_attention_tc_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (rc != cudaSuccess) return (int)rc;
         raised = true;
     }
-    const int rc = fl_launch(latent_attention_tc_kernel, dim3(n_tokens, (heads + 15) / 16, split_keys > 0 ? n_splits : 1),
-                             dim3(LT_WARPS * 32), smem, stream, (const bf16*)q, q_ld, out, out_ld, (const bf16*)cache,
-                             page_size, block_table, bt_stride, tok_req, positions, heads, window, scale, split_keys,
-                             partial);
+    int rc = 0;
+    FL_DISPATCH(out_dtype, TO,
+        rc = fl_launch(latent_attention_tc_kernel<TO>, dim3(n_tokens, (heads + 15) / 16, split_keys > 0 ? n_splits : 1),
+                       dim3(LT_WARPS * 32), smem, stream, (const bf16*)q, q_ld, (TO*)out, out_ld, (const bf16*)cache,
+                       page_size, block_table, bt_stride, tok_req, positions, heads, window, scale, split_keys, partial));
     if (rc || split_keys == 0) return rc;
-    return fl_launch(latent_merge_kernel, dim3(n_tokens, heads), dim3(128), 0, stream, (const float*)partial, out, out_ld,
-                     heads, n_splits);
+    FL_DISPATCH(out_dtype, TO,
+        return fl_launch(latent_merge_kernel<TO>, dim3(n_tokens, heads), dim3(128), 0, stream, (const float*)partial,
+                         (TO*)out, out_ld, heads, n_splits));
+    return 0;
 }

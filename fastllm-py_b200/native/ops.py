@@ -357,20 +357,20 @@ def latent_tc_library(rank: int, rot: int):
 
 def latent_attention_tc(q, out, cache, block_table, tok_req, positions, heads, rank, rot, window, scale, page_size,
                         split_keys=0, n_splits=1, partial=None):
-    """The same on tensor cores: q and cache bfloat16, out float32; one build per (rank, rot).  With
+    """The same on tensor cores: q and cache bfloat16, out float32 or bfloat16; one build per (rank, rot).  With
     `split_keys` (a multiple of 32) each token's keys are shared out over `n_splits` blocks, which must reach
     every token's last key ((longest visible span - 1) // split_keys + 2 does), and merged from `partial`
     (float32, N * heads * n_splits * (rank + 2))."""
     _require_cuda(q, out, cache, block_table, tok_req, positions)
-    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.float32:
-        raise KernelError("latent_attention_tc: q and cache bfloat16, out float32")
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("latent_attention_tc: q and cache must be bfloat16")
     name, defines = latent_tc_library(rank, rot)
     if split_keys and (partial is None or partial.numel() < q.shape[0] * heads * n_splits * (rank + 2)):
         raise KernelError("latent_attention_tc: the buffer for the splits' results is too small")
-    fn = _fn(name, "fl_latent_attention_tc", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_void_p, c_int,
+    fn = _fn(name, "fl_latent_attention_tc", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int,
                                               c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
                                               c_void_p], defines)
-    _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), page_size, _ptr(block_table), block_table.stride(0),
+    _check(fn(_ptr(q), _ld(q), _ptr(out), dtype_code(out), _ld(out), _ptr(cache), page_size, _ptr(block_table), block_table.stride(0),
               _ptr(tok_req), _ptr(positions), q.shape[0], heads, int(window or 0), float(scale), int(split_keys),
               int(n_splits), _ptr(partial), _stream()), "latent_attention_tc", 2 if split_keys else 1)
 
@@ -386,6 +386,21 @@ def gemm_simt_batched(a, a_batch, w, out, out_batch):
                                                    c_void_p, c_int, c_long, c_long, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(a), dtype_code(a), _ld(a), a_batch, _ptr(w), dtype_code(w), k, n * k, _ptr(out), dtype_code(out),
               _ld(out), out_batch, a.shape[0], n, k, batch, _stream()), "gemm_simt_batched")
+
+
+def gemm_batched(a, a_batch, w, out, out_batch):
+    """`gemm_simt_batched` with the kernel chosen by the operands: bfloat16 a and w with K a multiple of 32
+    and 16-byte aligned column blocks go to the tensor cores, everything else to the CUDA cores."""
+    batch, n, k = w.shape
+    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 32 == 0 and a_batch % 8 == 0 \
+            and _ld(a) % 8 == 0 and a.data_ptr() % 16 == 0 and w.is_contiguous():
+        _require_cuda(a, w, out)
+        fn = _fn("gemm_mma", "fl_gemm_mma_batched", [c_void_p, c_long, c_long, c_void_p, c_void_p, c_int, c_long, c_long,
+                                                     c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_ptr(a), _ld(a), a_batch, _ptr(w), _ptr(out), dtype_code(out), _ld(out), out_batch, a.shape[0], n, k,
+                  batch, _stream()), "gemm_mma_batched")
+        return
+    gemm_simt_batched(a, a_batch, w, out, out_batch)
 
 
 # ------------------------------------------------------------- routed experts

@@ -13,7 +13,9 @@ W_uk,h^T into latent space (q~ = [W_uk,h^T q_plain | q_rot], `kv_rank + rot_dim`
 elements), attention runs on the cache rows themselves, and the weighted sum of
 latents goes through W_uv,h: the same sums in another order, and the cache is
 read once for all heads.  The per-head products take W_uk and W_uv re-laid at
-load as [heads, kv_rank, dim] and [heads, vdim, kv_rank].
+load as [heads, kv_rank, dim] and [heads, vdim, kv_rank]; in bfloat16, with sizes
+that are multiples of 32, they and the attention itself run on the tensor cores
+(one batched launch each), else on the CUDA cores.
 
 A layer with `shares_cache` has no W_dkv: it reads the rows another layer's run
 wrote, with its own queries, W_uk, W_uv, window and scale.  The cache keeps what
@@ -37,7 +39,7 @@ class LatentAttention(Part):
     tensors: q [heads * (dim + rot_dim), hidden], uk [heads * dim, kv_rank], uv [heads * vdim, kv_rank],
     o [hidden, heads * vdim] and, unless shares_cache, dkv [kv_rank + rot_dim, hidden], dkv_norm [kv_rank]."""
     category = "mixer"
-    native_libraries = ("latent_attention",)
+    native_libraries = ("latent_attention", "gemm_mma")
     SPLIT_BELOW = 64                 # blocks (tokens x groups of 16 heads) under which a step's keys are split
     SCRATCH = "latent attention splits"
 
@@ -138,8 +140,8 @@ class LatentAttention(Part):
         cos, sin = self.position.tables()
         ops.latent_prep(proj, q, self.heads, self.dim, self.rot, self.rank, self.dkv_norm, self.norm_eps, cos, sin,
                         step.positions, cache.slots, cache.tensor if cache.writes else None)
-        ops.gemm_simt_batched(proj, self.dim + self.rot, self.uk_t, q, self.width)
-        mix = ws.rows("latent_mix", n, self.heads * self.rank, torch.float32)
+        ops.gemm_batched(proj, self.dim + self.rot, self.uk_t, q, self.width)
+        mix = ws.rows("latent_mix", n, self.heads * self.rank, dt if tc else torch.float32)
         if tc:
             if self.plan_key not in step.plans:               # a step built by hand, not by the engine
                 self.plan_step(step)
@@ -151,5 +153,5 @@ class LatentAttention(Part):
             ops.latent_attention(q, mix, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
                                  self.rank, self.rot, self.window, self.scale, cache.page_size)
         ctx = ws.rows("latent_ctx", n, self.heads * self.vdim, dt)
-        ops.gemm_simt_batched(mix, self.rank, self.uv, ctx, self.vdim)
+        ops.gemm_batched(mix, self.rank, self.uv, ctx, self.vdim)
         return self.o.forward(ctx, out, defer=True)

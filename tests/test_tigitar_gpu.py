@@ -280,6 +280,17 @@ def test_gated_unit_soft_cap_and_batched_product_kernels():
         ref = a[:, h * 11:h * 11 + 9] @ w[h].float().T
         assert float((out[:, h * 15:h * 15 + 13] - ref).abs().max()) <= 1e-4
         assert float(out[:, h * 15 + 13:(h + 1) * 15].abs().max()) == 0.0
+    # the same product on tensor cores: 5 heads of 64 + 16 columns, 150 outputs each, 70 and 3 rows
+    for rows in (70, 3):
+        a = torch.randn(rows, 5 * 80, device="cuda").to(torch.bfloat16)
+        w = torch.randn(5, 150, 64, device="cuda").to(torch.bfloat16)
+        for dt in (torch.float32, torch.bfloat16):
+            out = torch.zeros(rows, 5 * 152, device="cuda", dtype=dt)
+            ops.gemm_batched(a, 80, w, out, 152)
+            for h in range(5):
+                ref = a[:, h * 80:h * 80 + 64].float() @ w[h].float().T
+                assert float((out[:, h * 152:h * 152 + 150].float() - ref).abs().max()) <= (1e-3 if dt == torch.float32 else 0.15)
+                assert float(out[:, h * 152 + 150:(h + 1) * 152].abs().max()) == 0.0
 
 
 def test_router_kernel_choice_weights_and_ties():
