@@ -22,7 +22,7 @@
 #include "common.cuh"
 
 #define DELTA_PARTS 8            // lanes that share one value column
-#define DELTA_COLS 32            // value columns of a block
+#define DELTA_COLS 32            // value columns of a block (16 when that fills the GPU better)
 
 // One block per (token, unit): a unit is one query head, one key head (dim channels each) or one value
 // head (vdim channels, and the head's beta and decay), so that even a single token spreads over many SMs.
@@ -102,48 +102,91 @@ __global__ void delta_tail_kernel(const T* __restrict__ proj, long ld, float* __
     }
 }
 
-// One block: one request, one head, DELTA_COLS value columns.  Thread (col, part) keeps the elements
-// d = i * DELTA_PARTS + part of column `col` of S.  The tokens' inputs (k, q of the head, the block's v
-// columns, beta, decay) come through shared memory in chunks of DELTA_CHUNK tokens, the next chunk in
-// flight (cp.async) while this one is consumed: the recurrence itself never waits for global memory.
+// One block: one request, one head, DELTA_COLS value columns.  Thread (col, part) keeps the DPT elements
+// d = part * DPT + i of column `col` of S.  The tokens' inputs (k, q of the head, the block's v columns,
+// beta, decay) come through shared memory in chunks of DELTA_CHUNK tokens, the next chunk in flight
+// (cp.async) while this one is consumed: the recurrence never waits for global memory.  In shared memory
+// a part's k (and q) elements are contiguous and parts are DPT + 4 floats apart, so a thread fetches them
+// four at a time without bank conflicts.
 #define DELTA_CHUNK 16
+
+__device__ __forceinline__ void delta_cp16(float* smem, const float* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
 
 __device__ __forceinline__ void delta_cp4(float* smem, const float* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem));
 }
 
-template <int DPT>
-__global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
+template <int DPT, int COLS>
+__global__ void __launch_bounds__(COLS * DELTA_PARTS) delta_scan_kernel(
     float* __restrict__ work, long work_ld, float* __restrict__ state, long state_stride,
     const int* __restrict__ req_start, const int* __restrict__ req_ctx, const int* __restrict__ req_qlen,
     const int* __restrict__ req_slot, int heads, int kv_heads, int dim, int vdim) {
+    static_assert(DPT % 4 == 0, "a thread's elements are fetched four at a time");
     pdl_wait();
     pdl_trigger();
-    extern __shared__ float delta_in[];                      // [2][DELTA_CHUNK][k dim | q dim | v DELTA_COLS | beta | decay]
+    constexpr int PART = DPT + 4;                            // floats between parts
+    constexpr int KQ = DELTA_PARTS * PART;                   // k (and q) of one token
+    constexpr int PER_TOKEN = 2 * KQ + COLS + 4;       // k | q | v COLS | beta | decay | pad
+    extern __shared__ __align__(16) float delta_in[];        // [2][DELTA_CHUNK][PER_TOKEN]
     const int r = blockIdx.x / heads, h = blockIdx.x % heads;
     const int g = h / (heads / kv_heads);
     const int part = threadIdx.x & (DELTA_PARTS - 1), col = threadIdx.x / DELTA_PARTS;
-    const int j = blockIdx.y * DELTA_COLS + col;
+    const int j = blockIdx.y * COLS + col;
     const bool live = j < vdim;
     const int jj = live ? j : vdim - 1;                      // idle columns shadow the last one and store nothing
     const int start = req_start[r], qlen = req_qlen[r];
     float* s_col = state + (long)req_slot[r] * state_stride + ((long)h * vdim + jj) * dim;
     const int qk_cols = kv_heads * dim, hv = heads * vdim;
-    const int per_token = 2 * dim + DELTA_COLS + 2;
-    const int v0 = blockIdx.y * DELTA_COLS;
+    const int v0 = blockIdx.y * COLS;
+    for (int idx = threadIdx.x; idx < 2 * DELTA_CHUNK * PER_TOKEN; idx += blockDim.x) delta_in[idx] = 0.0f;   // (the gaps stay 0)
+    __syncthreads();
+    // rows whose pieces are all 16-byte aligned are copied four floats at a time, 128 slots a token
+    const bool wide = dim % 4 == 0 && vdim % 4 == 0 && v0 + COLS <= vdim && dim / 2 + COLS / 4 + 2 <= 128 && work_ld % 4 == 0;
     auto fetch = [&](int buf, int first) {                   // tokens first .. first + DELTA_CHUNK - 1 of the portion
-        float* dst = delta_in + (long)buf * DELTA_CHUNK * per_token;
+        float* dst = delta_in + (long)buf * DELTA_CHUNK * PER_TOKEN;
         const int n_tok = min(DELTA_CHUNK, qlen - first);
-        for (int idx = threadIdx.x; idx < n_tok * per_token; idx += blockDim.x) {
-            const int n = idx / per_token, e = idx % per_token;
+        if (wide) {
+            const int c = threadIdx.x & 127, quarter = dim / 4;
+            for (int n = threadIdx.x >> 7; n < n_tok; n += (COLS * DELTA_PARTS) >> 7) {
+                const float* row = work + (long)(start + first + n) * work_ld;
+                float* to = dst + (long)n * PER_TOKEN;
+                if (c < 2 * quarter) {                                            // k, then q
+                    const int d = (c < quarter ? c : c - quarter) * 4;
+                    delta_cp16(to + (c < quarter ? 0 : KQ) + (d / DPT) * PART + d % DPT,
+                               row + (c < quarter ? qk_cols : 0) + g * dim + d);
+                } else if (c < 2 * quarter + COLS / 4) {
+                    const int e = (c - 2 * quarter) * 4;
+                    delta_cp16(to + 2 * KQ + e, row + 2 * qk_cols + h * vdim + v0 + e);
+                } else if (c < 2 * quarter + COLS / 4 + 2) {                      // beta, decay
+                    const int e = c - 2 * quarter - COLS / 4;
+                    delta_cp4(to + 2 * KQ + COLS + e, row + 2 * qk_cols + hv + e * heads + h);
+                }
+            }
+            asm volatile("cp.async.commit_group;");
+            return;
+        }
+        const int wanted = 2 * dim + COLS + 2;
+        for (int idx = threadIdx.x; idx < n_tok * wanted; idx += blockDim.x) {
+            const int n = idx / wanted, e = idx % wanted;
             const float* row = work + (long)(start + first + n) * work_ld;
             const float* src;
-            if (e < dim) src = row + qk_cols + g * dim + e;                       // k
-            else if (e < 2 * dim) src = row + g * dim + (e - dim);                // q
-            else if (e < 2 * dim + DELTA_COLS) src = row + 2 * qk_cols + h * vdim + min(v0 + e - 2 * dim, vdim - 1);
-            else src = row + 2 * qk_cols + hv + (e - 2 * dim - DELTA_COLS) * heads + h;   // beta, decay
-            delta_cp4(dst + idx, src);
+            int at;
+            if (e < 2 * dim) {                                                    // k, then q
+                const int d = e < dim ? e : e - dim;
+                src = row + (e < dim ? qk_cols : 0) + g * dim + d;
+                at = (e < dim ? 0 : KQ) + (d / DPT) * PART + d % DPT;
+            } else if (e < 2 * dim + COLS) {
+                src = row + 2 * qk_cols + h * vdim + min(v0 + e - 2 * dim, vdim - 1);
+                at = 2 * KQ + (e - 2 * dim);
+            } else {                                                              // beta, decay
+                src = row + 2 * qk_cols + hv + (e - 2 * dim - COLS) * heads + h;
+                at = 2 * KQ + COLS + (e - 2 * dim - COLS);
+            }
+            delta_cp4(dst + (long)n * PER_TOKEN + at, src);
         }
         asm volatile("cp.async.commit_group;");
     };
@@ -152,7 +195,7 @@ __global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
     fetch(0, 0);
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = i * DELTA_PARTS + part;
+        const int d = part * DPT + i;
         S[i] = (!fresh && d < dim) ? s_col[d] : 0.0f;
     }
     float* o_base = work + (long)start * work_ld + 2 * qk_cols + hv + 2 * heads + h * vdim + j;
@@ -164,22 +207,23 @@ __global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
             asm volatile("cp.async.wait_group 0;");
         }
         __syncthreads();
-        const float* in = delta_in + (long)buf * DELTA_CHUNK * per_token;
+        const float* in = delta_in + (long)buf * DELTA_CHUNK * PER_TOKEN;
         const int n_tok = min(DELTA_CHUNK, qlen - first);
-        for (int n = 0; n < n_tok; ++n, in += per_token) {
+        for (int n = 0; n < n_tok; ++n, in += PER_TOKEN) {
             // With a = S^T k, b = S^T q (S before the token) and c = q . k:  u = beta (v - g a) and the
             // read-out of the updated state is g b + c u.  The three sums are independent, so their chains
             // and their reductions over the column's lanes overlap; only u stands between this token's
             // sums and the next token's.
             float k[DPT], a[2] = {0.0f, 0.0f}, bq[2] = {0.0f, 0.0f}, c[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                const int d = i * DELTA_PARTS + part;
-                k[i] = d < dim ? in[d] : 0.0f;
-                const float qv = d < dim ? in[dim + d] : 0.0f;
-                a[i & 1] += S[i] * k[i];
-                bq[i & 1] += S[i] * qv;
-                c[i & 1] += qv * k[i];
+            for (int i = 0; i < DPT; i += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(in + part * PART + i);
+                const float4 qv = *reinterpret_cast<const float4*>(in + KQ + part * PART + i);
+                k[i] = kv.x; k[i + 1] = kv.y; k[i + 2] = kv.z; k[i + 3] = kv.w;
+                a[0] += S[i] * kv.x;      bq[0] += S[i] * qv.x;      c[0] += qv.x * kv.x;
+                a[1] += S[i + 1] * kv.y;  bq[1] += S[i + 1] * qv.y;  c[1] += qv.y * kv.y;
+                a[0] += S[i + 2] * kv.z;  bq[0] += S[i + 2] * qv.z;  c[0] += qv.z * kv.z;
+                a[1] += S[i + 3] * kv.w;  bq[1] += S[i + 3] * qv.w;  c[1] += qv.w * kv.w;
             }
             float dot = a[0] + a[1], read = bq[0] + bq[1], qk = c[0] + c[1];
 #pragma unroll
@@ -188,8 +232,8 @@ __global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
                 read += __shfl_xor_sync(0xffffffffu, read, o);
                 qk += __shfl_xor_sync(0xffffffffu, qk, o);
             }
-            const float decay = in[2 * dim + DELTA_COLS + 1];
-            const float u = in[2 * dim + DELTA_COLS] * (in[2 * dim + col] - decay * dot);
+            const float decay = in[2 * KQ + COLS + 1];
+            const float u = in[2 * KQ + COLS] * (in[2 * KQ + col] - decay * dot);
 #pragma unroll
             for (int i = 0; i < DPT; ++i) S[i] = fmaf(k[i], u, decay * S[i]);
             if (live && part == 0) o_base[(long)(first + n) * work_ld] = decay * read + qk * u;
@@ -199,7 +243,7 @@ __global__ void __launch_bounds__(DELTA_COLS * DELTA_PARTS) delta_scan_kernel(
     if (live) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
-            const int d = i * DELTA_PARTS + part;
+            const int d = part * DPT + i;
             if (d < dim) s_col[d] = S[i];
         }
     }
@@ -262,20 +306,35 @@ FL_API int fl_delta_scan(float* work, long work_ld, float* state, long state_str
     if (n_requests <= 0) return 0;
     if (heads % kv_heads || dim < 1 || dim > 32 * DELTA_PARTS) return (int)cudaErrorInvalidValue;
     const int per_thread = (dim + DELTA_PARTS - 1) / DELTA_PARTS;
-    const size_t smem = (size_t)2 * DELTA_CHUNK * (2 * dim + DELTA_COLS + 2) * sizeof(float);     // <= 35 KB
-    dim3 grid(n_requests * heads, (vdim + DELTA_COLS - 1) / DELTA_COLS);
+    // a block takes 32 value columns, or 16 when blocks of 32 would leave most of the GPU idle (a lone
+    // request's prompt): the recurrence is a chain per token, so what counts is how many SMs walk it
+    const bool narrow = (long)n_requests * heads * ((vdim + 31) / 32) < 96 && vdim > 16;
+    const int cols = narrow ? 16 : DELTA_COLS;
+    dim3 grid(n_requests * heads, (vdim + cols - 1) / cols);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+#define FL_DELTA_SCAN_COLS(DPT, COLS)                                                                               \
+    {                                                                                                               \
+        const size_t smem = (size_t)2 * DELTA_CHUNK * (2 * DELTA_PARTS * (DPT + 4) + COLS + 4) * sizeof(float);     \
+        static bool raised = false;                                                                                 \
+        if (smem > 48 * 1024 && !raised) {                                                                          \
+            const cudaError_t rc = cudaFuncSetAttribute(delta_scan_kernel<DPT, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (rc != cudaSuccess) return (int)rc;                                                                  \
+            raised = true;                                                                                          \
+        }                                                                                                           \
+        return fl_launch(delta_scan_kernel<DPT, COLS>, grid, dim3(COLS * DELTA_PARTS), smem, stream, work, work_ld, state, \
+                         state_stride, req_start, req_ctx, req_qlen, req_slot, heads, kv_heads, dim, vdim);         \
+    }
 #define FL_DELTA_SCAN(DPT)                                                                                          \
-    if (per_thread <= DPT)                                                                                          \
-        return fl_launch(delta_scan_kernel<DPT>, grid, dim3(DELTA_COLS * DELTA_PARTS), smem, stream, work, work_ld, state, \
-                         state_stride, req_start, req_ctx, req_qlen, req_slot, heads, kv_heads, dim, vdim)
-    FL_DELTA_SCAN(2);
+    if (per_thread <= DPT) {                                                                                        \
+        if (narrow) FL_DELTA_SCAN_COLS(DPT, 16) else FL_DELTA_SCAN_COLS(DPT, 32)                                    \
+    }
     FL_DELTA_SCAN(4);
     FL_DELTA_SCAN(8);
     FL_DELTA_SCAN(12);
     FL_DELTA_SCAN(16);
     FL_DELTA_SCAN(24);
     FL_DELTA_SCAN(32);
+#undef FL_DELTA_SCAN_COLS
 #undef FL_DELTA_SCAN
     return (int)cudaErrorInvalidValue;
 }

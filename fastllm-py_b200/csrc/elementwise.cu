@@ -552,3 +552,53 @@ FL_API int fl_softcap(float* x, long ld, int n_rows, int cols, float cap, cudaSt
     if (n_rows > 65535) return (int)cudaErrorInvalidValue;
     return fl_launch(softcap_kernel, dim3((cols + 255) / 256, n_rows), dim3(256), 0, stream, x, ld, cols, cap);
 }
+
+// The same with the sublayer's output given as split-K partial sums (added in slab order and rounded to
+// the activation type first, as the separate reduction stores them): a decode step saves that kernel.
+template <typename TW, typename TO>
+__global__ void sandwich_norm_partial_kernel(float* __restrict__ x, long x_ld, const float* __restrict__ partial, int splits,
+                                             long split_stride, long ld, const TW* __restrict__ w_post, float eps_post,
+                                             const TW* __restrict__ w_pre, float eps_pre, TO* __restrict__ out, long out_ld,
+                                             int dim) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float sandwich_row[];               // [dim]: the sublayer's output, then the summed row
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* xr = x + (long)r * x_ld;
+    const float* pr = partial + (long)r * ld;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = to_f32<TO>(from_f32<TO>(sum_splits(pr, i, splits, split_stride)));
+        sandwich_row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv_post = 1.0f / sqrtf(ss / (float)dim + eps_post);
+    ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = xr[i] + sandwich_row[i] * inv_post * to_f32<TW>(w_post[i]);
+        xr[i] = v;
+        sandwich_row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv_pre = 1.0f / sqrtf(ss / (float)dim + eps_pre);
+    TO* o = out + (long)r * out_ld;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        o[i] = from_f32<TO>(sandwich_row[i] * inv_pre * to_f32<TW>(w_pre[i]));
+}
+
+FL_API int fl_sandwich_norm_partial(float* x, long x_ld, const float* partial, int splits, long split_stride, long ld,
+                                    const void* w_post, float eps_post, const void* w_pre, float eps_pre, int w_dtype,
+                                    void* out, int out_dtype, long out_ld, int n_rows, int dim, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if ((size_t)dim * sizeof(float) > 48 * 1024 || out == nullptr) return (int)cudaErrorInvalidValue;
+    int threads = (dim + 31) / 32 * 32;
+    threads = threads > 512 ? 512 : threads;
+    FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
+        return fl_launch(sandwich_norm_partial_kernel<TW, TO>, dim3(n_rows), dim3(threads), (size_t)dim * sizeof(float),
+                         stream, x, x_ld, partial, splits, split_stride, ld, (const TW*)w_post, eps_post,
+                         (const TW*)w_pre, eps_pre, (TO*)out, out_ld, dim)));
+    return 0;
+}

@@ -152,8 +152,8 @@ FL_API int fl_moe_experts(const void* h, int dtype, long h_ld, const void* w_gu,
 // two tensor-core products run over the tiles: a tile's rows share one expert's matrix.
 //
 //   moe_sort        one block: counts per expert, padded offsets, row -> pair, pair -> row, tile -> expert
-//   moe_group_mma   bfloat16 mma.sync m16n8k16, 64 rows x 128 weight rows per block, K in steps of 32 through
-//                   a two-stage cp.async ring.  GATED: the 128 weight rows are 64 gate rows and the 64 up rows
+//   moe_group_mma   bfloat16 mma.sync m16n8k16, 64 rows x 128 weight rows per block, K in steps of 64 through
+//                   a three-stage cp.async ring.  GATED: the 128 weight rows are 64 gate rows and the 64 up rows
 //                   of the same features, A rows are gathered token rows, the epilogue writes act(g) * u
 //                   (bfloat16, in row order); else A is that buffer and the output float [rows, width]
 //   moe_combine     out[t] = sum_k weight[t, k] * y[row of pair (t, k)], in order of choice
@@ -207,8 +207,10 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
 
-#define MOE_BK 32
-#define MOE_PITCH 40             // bfloat16 elements between rows of a staged tile: ldmatrix without bank conflicts
+#define MOE_BK 64
+#define MOE_STAGES 3
+#define MOE_PITCH 72             // bfloat16 elements between rows of a staged tile: ldmatrix without bank conflicts
+#define MOE_SMEM (MOE_STAGES * (MOE_TM + 128) * MOE_PITCH * 2)
 
 // grid: (tiles of rows, blocks of 64 features (GATED) or 128 columns).  K % 32 == 0, rows 16-byte aligned.
 template <bool GATED>
@@ -218,8 +220,9 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
     float* __restrict__ y_out, long out_ld, int act) {
     pdl_wait();
     pdl_trigger();
-    __shared__ __align__(16) bf16 a_s[2][MOE_TM][MOE_PITCH];
-    __shared__ __align__(16) bf16 w_s[2][128][MOE_PITCH];
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    bf16 (*a_s)[MOE_TM][MOE_PITCH] = reinterpret_cast<bf16 (*)[MOE_TM][MOE_PITCH]>(moe_smem);
+    bf16 (*w_s)[128][MOE_PITCH] = reinterpret_cast<bf16 (*)[128][MOE_PITCH]>(moe_smem + MOE_STAGES * MOE_TM * MOE_PITCH * 2);
     __shared__ int pair_s[MOE_TM];
     const int tile = blockIdx.x;
     if (tile >= *n_tiles) return;
@@ -228,8 +231,8 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
     const int wm = warp >> 2, wn = warp & 3;                    // 2 x 4 warps: 32 rows x (GATED: 16 + 16, else 32) columns
     if (tid < MOE_TM) pair_s[tid] = row_pair[tile * MOE_TM + tid];
     __syncthreads();
-    // sources of this thread's 16-byte pieces of a stage: one of A (64 rows x 4), two of W (128 rows x 4)
-    const int ar = tid >> 2, ac = (tid & 3) * 8;
+    // sources of this thread's 16-byte pieces of a stage: two of A (64 rows x 8), four of W (128 rows x 8)
+    const int ar = tid >> 2, ac = (tid & 3) * 16;
     const bf16* a_src;
     if (GATED) {
         const int pair = pair_s[ar];
@@ -255,9 +258,12 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
         w_src[i] = w + row * K + ac;
     }
     auto stage = [&](int buf, int k0) {
-        cp_async16(&a_s[buf][ar][ac], a_src + k0);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) cp_async16(&w_s[buf][(tid >> 2) + i * 64][ac], w_src[i] + k0);
+        for (int half = 0; half < 2; ++half) {
+            cp_async16(&a_s[buf][ar][ac + half * 8], a_src + k0 + half * 8);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) cp_async16(&w_s[buf][(tid >> 2) + i * 64][ac + half * 8], w_src[i] + k0 + half * 8);
+        }
         cp_async_commit();
     };
     float acc[2][4][4];
@@ -269,15 +275,12 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
             for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.0f;
     const int n_k = K / MOE_BK;
     stage(0, 0);
+    if (n_k > 1) stage(1, MOE_BK);
     for (int kb = 0; kb < n_k; ++kb) {
-        const int buf = kb & 1;
-        if (kb + 1 < n_k) {
-            stage(buf ^ 1, (kb + 1) * MOE_BK);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        const int buf = kb % MOE_STAGES;
+        if (kb + 1 < n_k) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncthreads();                                            // stage kb has landed; stage kb - 1 is read by no one
+        if (kb + 2 < n_k) stage((kb + 2) % MOE_STAGES, (kb + 2) * MOE_BK);
 #pragma unroll
         for (int ks = 0; ks < MOE_BK; ks += 16) {
             unsigned af[2][4], bfr[4][2];
@@ -306,7 +309,6 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
                                  : "+f"(acc[i][j][0]), "+f"(acc[i][j][1]), "+f"(acc[i][j][2]), "+f"(acc[i][j][3])
                                  : "r"(af[i][0]), "r"(af[i][1]), "r"(af[i][2]), "r"(af[i][3]), "r"(bfr[j][0]), "r"(bfr[j][1]));
         }
-        __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i)
@@ -360,6 +362,16 @@ FL_API int fl_moe_group_takes(int dtype, int w_dtype, int width, int ff) {
     return dtype == FL_BF16 && w_dtype == FL_BF16 && width % MOE_BK == 0 && ff % MOE_BK == 0;
 }
 
+static int moe_group_smem_ready() {
+    static int rc = -1;
+    if (rc < 0) {
+        rc = (int)cudaFuncSetAttribute(moe_group_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_SMEM);
+        if (rc == 0)
+            rc = (int)cudaFuncSetAttribute(moe_group_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_SMEM);
+    }
+    return rc;
+}
+
 // ints: row_pair [rows] | pair_row [n_tokens * top] | tile_expert [rows / 64] | n_tiles [1];
 // act: bfloat16 [rows, ff]; y: float [rows, width].
 FL_API int fl_moe_experts_grouped(const void* h, long h_ld, const void* w_gu, const void* w_down, const int* chosen,
@@ -373,14 +385,16 @@ FL_API int fl_moe_experts_grouped(const void* h, long h_ld, const void* w_gu, co
     int* tile_expert = pair_row + (long)n_tokens * top;
     int* n_tiles = tile_expert + max_tiles;
     if ((size_t)(2 * experts + 1) * sizeof(int) > 48 * 1024 || ((uintptr_t)h % 16) || (h_ld % 8)) return (int)cudaErrorInvalidValue;
-    int rc = fl_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, chosen,
+    int rc = moe_group_smem_ready();
+    if (rc) return rc;
+    rc = fl_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, chosen,
                        n_tokens * top, experts, row_pair, pair_row, tile_expert, n_tiles, max_tiles);
     if (rc) return rc;
-    rc = fl_launch(moe_group_mma_kernel<true>, dim3(max_tiles, (ff + 63) / 64), dim3(256), 0, stream, (const bf16*)h, h_ld,
+    rc = fl_launch(moe_group_mma_kernel<true>, dim3(max_tiles, (ff + 63) / 64), dim3(256), MOE_SMEM, stream, (const bf16*)h, h_ld,
                    (const bf16*)w_gu, ff, width, (const int*)row_pair, (const int*)tile_expert, (const int*)n_tiles, top,
                    (bf16*)act, (float*)nullptr, (long)ff, act_code);
     if (rc) return rc;
-    rc = fl_launch(moe_group_mma_kernel<false>, dim3(max_tiles, (width + 127) / 128), dim3(256), 0, stream,
+    rc = fl_launch(moe_group_mma_kernel<false>, dim3(max_tiles, (width + 127) / 128), dim3(256), MOE_SMEM, stream,
                    (const bf16*)act, (long)ff, (const bf16*)w_down, width, ff, (const int*)row_pair,
                    (const int*)tile_expert, (const int*)n_tiles, top, (bf16*)nullptr, y, (long)width, act_code);
     if (rc) return rc;

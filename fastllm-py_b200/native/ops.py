@@ -258,6 +258,20 @@ def sandwich_norm(resid, y, w_post, eps_post, w_pre, eps_pre, out, rows=None):
               0 if out is None else _ld(out), n_rows, resid.shape[1], _ptr(rows), _stream()), "sandwich_norm")
 
 
+def sandwich_norm_partial(resid, partial, w_post, eps_post, w_pre, eps_pre, out):
+    """`sandwich_norm` with the sublayer's output given as split-K partial sums (added in slab order)."""
+    partial.check()
+    _require_cuda(resid, w_post, w_pre, out)
+    if resid.dtype != torch.float32 or w_pre.dtype != w_post.dtype:
+        raise KernelError("sandwich_norm_partial: float32 residual stream, norm weights of one dtype")
+    fn = _fn("elementwise", "fl_sandwich_norm_partial", [c_void_p, c_long, c_void_p, c_int, c_long, c_long, c_void_p,
+                                                         c_float, c_void_p, c_float, c_int, c_void_p, c_int, c_long,
+                                                         c_int, c_int, c_void_p])
+    _check(fn(_ptr(resid), _ld(resid), _ptr(partial.data), partial.splits, partial.split_stride, partial.ld,
+              _ptr(w_post), float(eps_post), _ptr(w_pre), float(eps_pre), dtype_code(w_post), _ptr(out),
+              dtype_code(out), _ld(out), resid.shape[0], resid.shape[1], _stream()), "sandwich_norm_partial")
+
+
 def softcap(logits, cap: float):
     """logits <- cap * tanh(logits / cap), in place (float32)."""
     _require_cuda(logits)

@@ -106,7 +106,9 @@ class ResidualStream:
         """`norm.apply(self, out, rows)`, with a pending sum that the norm can take."""
         pending = self.pending
         if pending is not None and not isinstance(pending, torch.Tensor):
-            if rows is not None or self.pending_norm is not None or not getattr(norm, "takes_partial", False):
+            both = getattr(norm, "takes_partial", False) and \
+                (self.pending_norm is None or getattr(norm, "takes_post_norm", False))
+            if rows is not None or not both:
                 pending = self.pending = pending.reduce_into(self.spill())
         if pending is not None and self.pending_norm is not None and not getattr(norm, "takes_post_norm", False):
             self.pending_norm.add_normed(self)           # x += norm(pending), for a norm that cannot do it itself

@@ -36,7 +36,10 @@ class RMSNorm(Part):
         post = getattr(stream, "pending_norm", None)
         if stream.pending is not None and post is not None:
             # x += post(pending); out = self(x): the layer norms the sublayer's output before adding it
-            ops.sandwich_norm(stream.x, stream.pending, post.weight, post.eps, self.weight, self.eps, out, rows)
+            if not isinstance(stream.pending, torch.Tensor):         # split-K partial sums (never with rows)
+                ops.sandwich_norm_partial(stream.x, stream.pending, post.weight, post.eps, self.weight, self.eps, out)
+            else:
+                ops.sandwich_norm(stream.x, stream.pending, post.weight, post.eps, self.weight, self.eps, out, rows)
             if rows is None:
                 stream.pending = stream.pending_norm = None
             return
