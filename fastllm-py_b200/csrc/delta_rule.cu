@@ -142,8 +142,11 @@ __global__ void __launch_bounds__(COLS * DELTA_PARTS) delta_scan_kernel(
     float* s_col = state + (long)req_slot[r] * state_stride + ((long)h * vdim + jj) * dim;
     const int qk_cols = kv_heads * dim, hv = heads * vdim;
     const int v0 = blockIdx.y * COLS;
-    for (int idx = threadIdx.x; idx < 2 * DELTA_CHUNK * PER_TOKEN; idx += blockDim.x) delta_in[idx] = 0.0f;   // (the gaps stay 0)
-    __syncthreads();
+    if (dim < DELTA_PARTS * DPT) {                           // the k and q places beyond dim are read: they stay 0
+        const int used = (qlen < DELTA_CHUNK ? qlen : 2 * DELTA_CHUNK) * PER_TOKEN;
+        for (int idx = threadIdx.x; idx < used; idx += blockDim.x) delta_in[idx] = 0.0f;
+        __syncthreads();
+    }
     // rows whose pieces are all 16-byte aligned are copied four floats at a time, 128 slots a token
     const bool wide = dim % 4 == 0 && vdim % 4 == 0 && v0 + COLS <= vdim && dim / 2 + COLS / 4 + 2 <= 128 && work_ld % 4 == 0;
     auto fetch = [&](int buf, int first) {                   // tokens first .. first + DELTA_CHUNK - 1 of the portion
