@@ -136,7 +136,12 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // silu(g) * u with the fast exponential and division: the epilogue has a fixed budget per tile (the
 // next tile's MMAs), and the exact forms cost five times the instructions for digits that a
 // bfloat16 result cannot hold (relative error about 1e-6 against bfloat16's 4e-3).
-__device__ __forceinline__ float gated_act(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+// `act` (the same in every thread of a launch): 0 silu, 1 relu, 2 gelu in its tanh form.
+__device__ __forceinline__ float gated_act(float g, float u, int act) {
+    if (act == 1) return fmaxf(g, 0.0f) * u;
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
 
 // A barrier among the four epilogue warps only (hardware barrier 1; barrier 0 is __syncthreads).
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -212,7 +217,7 @@ template <int BN, int STAGES, typename OutT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, float* __restrict__ partial, long ld_partial, int M, int N, int K,
-    int kb_per_split, int* __restrict__ status, int gate_rows, int feat, int wp) {
+    int kb_per_split, int* __restrict__ status, int gate_rows, int feat, int wp, int act) {
     using L = TcSmem<BN, STAGES>;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ unsigned char smem_raw[];
@@ -379,14 +384,14 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
                         if (sizeof(OutT) == 2 && vec_ok && f0 + f + 8 <= N) {
                             const float4 g0 = *reinterpret_cast<const float4*>(xg), g1 = *reinterpret_cast<const float4*>(xg + 4);
                             const float4 u0 = *reinterpret_cast<const float4*>(xg + feat), u1 = *reinterpret_cast<const float4*>(xg + feat + 4);
-                            const OutT v[8] = {from_f32<OutT>(gated_act(g0.x, u0.x)), from_f32<OutT>(gated_act(g0.y, u0.y)),
-                                               from_f32<OutT>(gated_act(g0.z, u0.z)), from_f32<OutT>(gated_act(g0.w, u0.w)),
-                                               from_f32<OutT>(gated_act(g1.x, u1.x)), from_f32<OutT>(gated_act(g1.y, u1.y)),
-                                               from_f32<OutT>(gated_act(g1.z, u1.z)), from_f32<OutT>(gated_act(g1.w, u1.w))};
+                            const OutT v[8] = {from_f32<OutT>(gated_act(g0.x, u0.x, act)), from_f32<OutT>(gated_act(g0.y, u0.y, act)),
+                                               from_f32<OutT>(gated_act(g0.z, u0.z, act)), from_f32<OutT>(gated_act(g0.w, u0.w, act)),
+                                               from_f32<OutT>(gated_act(g1.x, u1.x, act)), from_f32<OutT>(gated_act(g1.y, u1.y, act)),
+                                               from_f32<OutT>(gated_act(g1.z, u1.z, act)), from_f32<OutT>(gated_act(g1.w, u1.w, act))};
                             *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(v);
                         } else {
                             for (int j = 0; j < 8 && f0 + f + j < N; ++j)
-                                dst[j] = from_f32<OutT>(gated_act(xg[j], xg[feat + j]));
+                                dst[j] = from_f32<OutT>(gated_act(xg[j], xg[feat + j], act));
                         }
                     }
                 }
@@ -636,7 +641,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, int M, int N, int K, int tiles_n, int num_tiles,
     int* __restrict__ status, int gate_rows, int splits, int kb_per_split, float* __restrict__ partial,
-    long ld_partial, const TcRope rope, int wp, int wt) {
+    long ld_partial, const TcRope rope, int wp, int wt, int act) {
     using L = Tc2<BNT>;
     static_assert(!GATED || BNT == 256, "the gated epilogue is written for 256-token tiles");
     static_assert(!ROPE || (!GATED && sizeof(OutT) == 2), "the rotary epilogue writes bfloat16 and is not gated");
@@ -823,7 +828,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                         if ((j & 1) != mine) continue;
                         const float own = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
                         const float other = x[j * 64 + col];
-                        st[j * 64 + col] = from_f32<OutT>(is_up ? gated_act(other, own) : gated_act(own, other));
+                        st[j * 64 + col] = from_f32<OutT>(is_up ? gated_act(other, own, act) : gated_act(own, other, act));
                     }
                     epilogue_sync();                        // the 32 x 64 results leave as whole rows
                     if (f0 < N)
@@ -925,7 +930,7 @@ template <int BNT, typename OutT, bool GATED = false, bool ROPE = false>
 static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M, int N,
                           int K, int num_sms, int* status, cudaStream_t stream, int gate_rows = 0, int splits = 1,
                           int kb_per_split = 0, float* partial = nullptr, long ld_partial = 0,
-                          const TcRope* rope_args = nullptr, int wp = 0) {
+                          const TcRope* rope_args = nullptr, int wp = 0, int act = 0) {
     static bool configured = false;
     auto kernel = gemm_tc_pair_kernel<BNT, OutT, GATED, ROPE>;
     TcRope rope = {};
@@ -957,7 +962,7 @@ static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, vo
     // Launched in plain stream order (no programmatic overlap with its neighbours): see the note in the kernel.
     cfg.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, (OutT*)C, ldc, M, N, K, tiles_n, num_tiles, status,
-                                   gate_rows, splits, kb_per_split, partial, ld_partial, rope, wp, wt);
+                                   gate_rows, splits, kb_per_split, partial, ld_partial, rope, wp, wt, act);
 }
 
 template <typename OutT>
@@ -1078,7 +1083,8 @@ static int make_w_map(CUtensorMap* map, const void* W, long rows, long K, long l
 template <int BN, int STAGES, typename OutT, bool GATED = false>
 static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc,
                      float* partial, long ld_partial, int M, int N, int K, int splits,
-                     int kb_per_split, int* status, cudaStream_t stream, int gate_rows = 0, int feat = 64, int wp = 0) {
+                     int kb_per_split, int* status, cudaStream_t stream, int gate_rows = 0, int feat = 64, int wp = 0,
+                     int act = 0) {
     using L = TcSmem<BN, STAGES>;
     // This kernel is launched with programmatic overlap, so CTAs of it and of its neighbours in the stream share
     // SMs; as many of them as fit an SM by shared memory must find their tensor-memory columns free at once, or an
@@ -1100,7 +1106,7 @@ static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C
     }
     dim3 grid(GATED ? (N + feat - 1) / feat : (N + TC_BM - 1) / TC_BM, (M + BN - 1) / BN, splits);
     return fl_launch(kernel, grid, dim3(TC_THREADS), (size_t)L::TOTAL, stream, map_w, map_a, (OutT*)C, ldc,
-                     partial, ld_partial, M, N, K, kb_per_split, status, gate_rows, feat, wp);
+                     partial, ld_partial, M, N, K, kb_per_split, status, gate_rows, feat, wp, act);
 }
 
 template <typename OutT>
@@ -1295,9 +1301,11 @@ FL_API int fl_gemm_tc_partial(const void* A, long lda, const void* W, long ldw, 
 // fused kernel was launched, -1 when this problem is not taken (too few features to fill the GPU
 // without a K split, or many tokens and a plan that splits K): the caller then runs the product
 // and the activation apart.
-FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int I,
-                             int K, int num_sms, int* status, cudaStream_t stream) {
+// (`act`: the gate's activation, 0 silu, 1 relu, 2 gelu in its tanh form.)
+FL_API int fl_gemm_tc_glu(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int I,
+                          int K, int act, int num_sms, int* status, cudaStream_t stream) {
     if (M <= 0 || I <= 0) return 0;
+    if (act < 0 || act > 2) return (int)cudaErrorInvalidValue;
     if (K <= 0) return (int)cudaErrorInvalidValue;
     // Up to 128 tokens: the one-tile kernel with as few features per CTA (16 to 64 in steps of 8) as
     // still leave every CTA a place on the SMs at once (two per SM); declined when even that gives too
@@ -1321,15 +1329,20 @@ FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, v
     rc = make_map(&map_a, A, M, K, lda, bn > 256 ? tc_pair_tile_tokens(M, 256) / 2 : bn);
     if (rc) return rc;
     if (bn == 512)
-        return launch_tc_pair<256, bf16, true>(map_w, map_a, C, ldc, M, I, K, num_sms, status, stream, I, 1, 0, nullptr, 0, nullptr, wp);
+        return launch_tc_pair<256, bf16, true>(map_w, map_a, C, ldc, M, I, K, num_sms, status, stream, I, 1, 0, nullptr, 0, nullptr, wp, act);
     const int kb = (K + TC_BK - 1) / TC_BK;
     switch (bn) {
-        case 16: return launch_tc<16, 6, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat, wp);
-        case 32: return launch_tc<32, 5, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat, wp);
-        case 64: return launch_tc<64, 4, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat, wp);
-        case 128: return launch_tc<128, 3, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat, wp);
+        case 16: return launch_tc<16, 6, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat, wp, act);
+        case 32: return launch_tc<32, 5, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat, wp, act);
+        case 64: return launch_tc<64, 4, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat, wp, act);
+        case 128: return launch_tc<128, 3, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat, wp, act);
     }
     return -1;
+}
+
+FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int I,
+                             int K, int num_sms, int* status, cudaStream_t stream) {
+    return fl_gemm_tc_glu(A, lda, W, ldw, C, ldc, M, I, K, 0, num_sms, status, stream);
 }
 
 // The q|k|v product of an attention layer with its rotary encoding and cache write in the epilogue (see TcRope):

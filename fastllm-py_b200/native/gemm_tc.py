@@ -28,9 +28,9 @@ def _lib():
         lib.fl_gemm_tc_plan_for.argtypes = [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int),
                                             ctypes.POINTER(c_int)]
         lib.fl_gemm_tc_plan_for.restype = None
-        lib.fl_gemm_tc_swiglu.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
-                                          c_int, c_int, c_void_p, c_void_p]
-        lib.fl_gemm_tc_swiglu.restype = c_int
+        lib.fl_gemm_tc_glu.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
+                                       c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.fl_gemm_tc_glu.restype = c_int
         lib.fl_gemm_tc_qkv_rope.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_long, c_int, c_int, c_void_p, c_void_p]
@@ -252,11 +252,11 @@ def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
     return partial
 
 
-def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor) -> bool:
-    """out[M, I] = silu(a @ gate^T) * (a @ up^T) for w = [gate; up] stacked as [2 I, K], all
-    bfloat16, in one kernel (the activation in the product's epilogue).  Returns False, having
-    done nothing, when the kernel does not take the problem (its plan splits K)."""
-    key = ("swiglu", a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, out.data_ptr(), out.shape,
+def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor, activation: str = "silu") -> bool:
+    """out[M, I] = act(a @ gate^T) * (a @ up^T) for w = [gate; up] stacked as [2 I, K], all
+    bfloat16, in one kernel (the activation in the product's epilogue; silu, relu or gelu_tanh).
+    Returns False, having done nothing, when the kernel does not take the problem (its plan splits K)."""
+    key = ("glu", activation, a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, out.data_ptr(), out.shape,
            out.stride(0), out.dtype)
     known = _launches.get(key)                              # (see gemm)
     if known is not None:
@@ -279,8 +279,8 @@ def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor) -> bool:
         w_ptr, ldw = _weight_args(w)
     except ops.KernelError:
         return False
-    fn = _lib().fl_gemm_tc_swiglu
-    args = (ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops._ld(out), m, inter, k,
+    fn = _lib().fl_gemm_tc_glu
+    args = (ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops._ld(out), m, inter, k, ops.activation_code(activation),
             _num_sms(a.device), ops._ptr(status_word(a.device)))
     rc = fn(*args, ops._stream())
     if rc == -1:

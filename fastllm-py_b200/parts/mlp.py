@@ -2,9 +2,9 @@
 
 fastllm_py/model.py:432-435 with the activation of
 fastllm_py/kernels/ops.py:157-163: g / (1 + exp(-g)) * u in float.  gate and up
-are stacked into one matrix so that one product serves both.  Other activations
-(`activation`: "relu", "gelu_tanh") take the unfused path: product, then one
-activation kernel."""
+are stacked into one matrix so that one product serves both, with the activation
+(`activation`: "silu", "relu", "gelu_tanh") in the product's epilogue where the
+tensor-core kernel takes the problem, else product and one activation kernel."""
 from __future__ import annotations
 
 from ..native import ops
@@ -48,7 +48,7 @@ class SwiGLU(Part):
         dt = self.ctx.dtype
         act = step.workspace.rows("ffn_act", n, self.inter, dt)
         silu = self.activation == "silu"
-        if silu and self.gate_up.forward_gated(h, act):      # product and activation in one kernel
+        if self.gate_up.forward_gated(h, act, self.activation):      # product and activation in one kernel
             return self.down.forward(act, out, defer=True)
         gu = step.workspace.rows("gate_up", n, 2 * self.inter, dt)
         partial = self.gate_up.forward(h, gu, defer=silu)

@@ -352,3 +352,26 @@ def test_tensor_core_latent_attention_against_the_cuda_core_kernel(rank, rot, he
     for result in (got, split):
         assert float((result - want).abs().max()) <= 2e-2
         assert float((result - want).abs().mean()) <= 2e-3
+
+
+def test_gated_product_with_relu_and_gelu_in_its_epilogue():
+    """The tensor-core product that applies the gate's activation itself, for the activations beside silu,
+    in its one-tile form (a decode-sized step) and its CTA-pair form (a prompt-sized step)."""
+    from fastllm_py_b200.native import gemm_tc
+
+    torch.manual_seed(5)
+    acts = {"relu": torch.relu, "gelu_tanh": lambda z: torch.nn.functional.gelu(z, approximate="tanh"),
+            "silu": torch.nn.functional.silu}
+    taken = 0
+    for m, inter, k in ((48, 1536, 256), (2048, 4096, 512)):
+        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(2 * inter, k, device="cuda") * k ** -0.5).to(torch.bfloat16)
+        for name, fn in acts.items():
+            out = torch.zeros(m, inter, device="cuda", dtype=torch.bfloat16)
+            if not gemm_tc.gemm_swiglu(a, w, out, name):
+                continue
+            taken += 1
+            prod = a.float() @ w.float().T
+            ref = fn(prod[:, :inter]) * prod[:, inter:]
+            assert float((out.float() - ref).abs().max()) <= 0.03 * float(ref.abs().max()) + 1e-2, (m, name)
+    assert taken >= 3
