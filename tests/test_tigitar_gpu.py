@@ -233,6 +233,27 @@ def test_trace_program_on_a_folder(made, tmp_path):
     assert worst(got, m["want"]) <= 2e-4 * max(1.0, top)
 
 
+def test_command_line_on_a_random_weights_folder(tmp_path):
+    """bin/make_model writes a folder from a configuration, bin/generate loads it by its architecture
+    string and generates through the scheduler."""
+    import json
+    import subprocess
+    import sys
+
+    raw = tt.config([(tt.delta(2, 1, 16, 16, 3), tt.moe(4, 2, 16)), (tt.latent(2, 16, 16, 16, 32, window=20), tt.dense(32))],
+                    width=32, vocab=64)
+    (tmp_path / "config.json").write_text(json.dumps(raw))
+    made_ = subprocess.run([sys.executable, str(replay.ROOT / "bin" / "make_model"), str(tmp_path / "config.json"),
+                            str(tmp_path / "m"), "--seed", "4", "--std", "0.2"], capture_output=True, text=True)
+    assert made_.returncode == 0 and "Tigitar" in made_.stdout, made_.stderr
+    run = subprocess.run([sys.executable, str(replay.ROOT / "bin" / "generate"), str(tmp_path / "m"), "-", "9",
+                          "bfloat16", "--random-prompt", "30", "--seed", "1"], capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr[-2000:]
+    lines = run.stdout.strip().splitlines()
+    assert "Tigitar: 2L width=32" in lines[0]
+    assert len([int(t) for t in lines[1].split(",")]) == 9
+
+
 # ------------------------------------------------------------------ kernels alone
 
 def test_norm_add_norm_kernel():
