@@ -35,8 +35,14 @@ MODELS = {
                         (tt.latent(2, 16, 6, 12, 9, window=None), tt.dense(20)),
                         (tt.latent(2, 8, 6, 4, 9, window=1, kv_from=4), tt.dense(20))],
                 vocab=61, width=36, eps=1e-6, softcap=None, page=16),
+    # sizes that the tensor-core kernels take in bfloat16 (latent attention with split keys in decode steps,
+    # the per-head products, the grouped expert products from 64 prompt tokens on)
+    "even": dict(layers=[(tt.latent(3, 32, 16, 32, 32, window=40), tt.moe(4, 2, 64)),
+                         (tt.delta(2, 2, 32, 32, 4), tt.dense(128)),
+                         (tt.latent(20, 32, 16, 16, 32, window=70, kv_from=0), tt.moe(4, 2, 64))],
+                 vocab=80, width=64, eps=1e-6, softcap=20.0, page=16),
 }
-LENGTHS = {"mix": [1, 2, 9, 23, 40, 77], "odd": [3, 30, 64, 51]}
+LENGTHS = {"mix": [1, 2, 9, 23, 40, 77], "odd": [3, 30, 64, 51], "even": [150, 70, 90]}
 
 
 @pytest.fixture(scope="module")
@@ -255,6 +261,48 @@ def test_command_line_on_a_random_weights_folder(tmp_path):
 
 
 # ------------------------------------------------------------------ kernels alone
+
+def test_grouped_expert_products_against_the_per_token_kernels():
+    from fastllm_py_b200.native import ops
+
+    torch.manual_seed(8)
+    n, width, ff, experts, top = 210, 128, 192, 5, 2
+    h = torch.randn(n, width, device="cuda").to(torch.bfloat16)
+    gate_up = (torch.randn(experts, 2 * ff, width, device="cuda") * width ** -0.5).to(torch.bfloat16)
+    down = (torch.randn(experts, width, ff, device="cuda") * ff ** -0.5).to(torch.bfloat16)
+    chosen = torch.stack([torch.randperm(experts, device="cuda")[:top] for _ in range(n)]).to(torch.int32)
+    chosen[:40] = torch.tensor([3, 1], dtype=torch.int32)              # one expert with many rows, one with none
+    chosen[chosen == 4] = 0
+    weights = torch.rand(n, top, device="cuda")
+    want = torch.empty(n, width, device="cuda", dtype=torch.bfloat16)
+    ops.moe_experts(h, gate_up, down, chosen, weights, torch.empty(n * top, ff, device="cuda"), want, "silu")
+    rows = ops.moe_group_rows(n, top, experts)
+    assert ops.moe_group_takes(torch.bfloat16, torch.bfloat16, width, ff)
+    ints = torch.empty(rows + n * top + rows // 64 + 1, dtype=torch.int32, device="cuda")
+    got = torch.empty_like(want)
+    ops.moe_experts_grouped(h, gate_up, down, chosen, weights, ints, torch.empty(rows, ff, device="cuda", dtype=torch.bfloat16),
+                            torch.empty(rows, width, device="cuda"), got, "silu")
+    torch.cuda.synchronize()
+    assert float((got.float() - want.float()).abs().max()) <= 0.03 * float(want.float().abs().max())
+    assert float((got.float() - want.float()).abs().mean()) <= 3e-3 * float(want.float().abs().max())
+
+
+def test_norm_add_norm_from_partial_sums():
+    from fastllm_py_b200.native import gemm_tc, ops
+
+    torch.manual_seed(9)
+    rows, dim, splits = 5, 72, 3
+    slabs = torch.randn(splits, rows, dim, device="cuda")
+    x = torch.randn(rows, dim, device="cuda")
+    wa, wb = (1 + 0.2 * torch.randn(2, dim, device="cuda")).to(torch.bfloat16)
+    partial = gemm_tc.Partial(slabs, splits, rows, dim, dim, slabs.device)
+    y = torch.empty(rows, dim, device="cuda", dtype=torch.bfloat16)
+    partial.reduce_into(y)
+    want_x, want = x.clone(), torch.empty(rows, dim, device="cuda", dtype=torch.bfloat16)
+    ops.sandwich_norm(want_x, y, wa, 1e-5, wb, 1e-6, want)
+    got = torch.empty_like(want)
+    ops.sandwich_norm_partial(x, partial, wa, 1e-5, wb, 1e-6, got)
+    assert torch.equal(x, want_x) and torch.equal(got, want)
 
 def test_norm_add_norm_kernel():
     from fastllm_py_b200.native import ops
