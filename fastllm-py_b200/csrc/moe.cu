@@ -152,7 +152,7 @@ FL_API int fl_moe_experts(const void* h, int dtype, long h_ld, const void* w_gu,
 // two tensor-core products run over the tiles: a tile's rows share one expert's matrix.
 //
 //   moe_sort        one block: counts per expert, padded offsets, row -> pair, pair -> row, tile -> expert
-//   moe_group_mma   bfloat16 mma.sync m16n8k16, 64 rows x 128 weight rows per block, K in steps of 64 through
+//   moe_group_mma   bfloat16 mma.sync m16n8k16, 64 rows x 128 weight rows per block, K in steps of 32 through
 //                   a three-stage cp.async ring.  GATED: the 128 weight rows are 64 gate rows and the 64 up rows
 //                   of the same features, A rows are gathered token rows, the epilogue writes act(g) * u
 //                   (bfloat16, in row order); else A is that buffer and the output float [rows, width]
@@ -207,9 +207,10 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
 
-#define MOE_BK 64
+#define MOE_BK 32
 #define MOE_STAGES 3
-#define MOE_PITCH 72             // bfloat16 elements between rows of a staged tile: ldmatrix without bank conflicts
+#define MOE_PITCH (MOE_BK + 8)   // bfloat16 elements between rows of a staged tile: ldmatrix without bank conflicts
+#define MOE_PIECES (MOE_BK / 32) // 16-byte pieces of a row that a thread copies per stage
 #define MOE_SMEM (MOE_STAGES * (MOE_TM + 128) * MOE_PITCH * 2)
 
 // grid: (tiles of rows, blocks of 64 features (GATED) or 128 columns).  K % 32 == 0, rows 16-byte aligned.
@@ -231,8 +232,8 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
     const int wm = warp >> 2, wn = warp & 3;                    // 2 x 4 warps: 32 rows x (GATED: 16 + 16, else 32) columns
     if (tid < MOE_TM) pair_s[tid] = row_pair[tile * MOE_TM + tid];
     __syncthreads();
-    // sources of this thread's 16-byte pieces of a stage: two of A (64 rows x 8), four of W (128 rows x 8)
-    const int ar = tid >> 2, ac = (tid & 3) * 16;
+    // sources of this thread's 16-byte pieces of a stage: its part of one row of A and of two rows of W
+    const int ar = tid >> 2, ac = (tid & 3) * 8 * MOE_PIECES;
     const bf16* a_src;
     if (GATED) {
         const int pair = pair_s[ar];
@@ -259,7 +260,7 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
     }
     auto stage = [&](int buf, int k0) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < MOE_PIECES; ++half) {
             cp_async16(&a_s[buf][ar][ac + half * 8], a_src + k0 + half * 8);
 #pragma unroll
             for (int i = 0; i < 2; ++i) cp_async16(&w_s[buf][(tid >> 2) + i * 64][ac + half * 8], w_src[i] + k0 + half * 8);
