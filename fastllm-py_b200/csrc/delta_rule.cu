@@ -196,10 +196,20 @@ __global__ void __launch_bounds__(COLS * DELTA_PARTS) delta_scan_kernel(
     float S[DPT];
     const bool fresh = req_ctx[r] == 0;
     fetch(0, 0);
+    // every thread's elements exist and every column starts on 16 bytes: four at a time
+    const bool whole = dim == DELTA_PARTS * DPT && state_stride % 4 == 0;
+    if (whole && !fresh) {
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-        const int d = part * DPT + i;
-        S[i] = (!fresh && d < dim) ? s_col[d] : 0.0f;
+        for (int i = 0; i < DPT; i += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(s_col + part * DPT + i);
+            S[i] = v.x; S[i + 1] = v.y; S[i + 2] = v.z; S[i + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = part * DPT + i;
+            S[i] = (!fresh && d < dim) ? s_col[d] : 0.0f;
+        }
     }
     float* o_base = work + (long)start * work_ld + 2 * qk_cols + hv + 2 * heads + h * vdim + j;
     for (int first = 0, buf = 0; first < qlen; first += DELTA_CHUNK, buf ^= 1) {
@@ -243,7 +253,11 @@ __global__ void __launch_bounds__(COLS * DELTA_PARTS) delta_scan_kernel(
         }
         __syncthreads();                                     // the chunk is overwritten by the fetch after next
     }
-    if (live) {
+    if (live && whole) {
+#pragma unroll
+        for (int i = 0; i < DPT; i += 4)
+            *reinterpret_cast<float4*>(s_col + part * DPT + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+    } else if (live) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = part * DPT + i;

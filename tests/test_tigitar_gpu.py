@@ -266,7 +266,7 @@ def test_grouped_expert_products_against_the_per_token_kernels():
     from fastllm_py_b200.native import ops
 
     torch.manual_seed(8)
-    n, width, ff, experts, top = 210, 128, 192, 5, 2
+    n, width, ff, experts, top = 210, 128, 160, 5, 2
     h = torch.randn(n, width, device="cuda").to(torch.bfloat16)
     gate_up = (torch.randn(experts, 2 * ff, width, device="cuda") * width ** -0.5).to(torch.bfloat16)
     down = (torch.randn(experts, width, ff, device="cuda") * ff ** -0.5).to(torch.bfloat16)
@@ -389,7 +389,7 @@ def test_router_kernel_choice_weights_and_ties():
     assert two.tolist() == [[0, 1, 2, 3]] * 2
 
 
-@pytest.mark.parametrize("rank,rot,heads,window", [(96, 16, 4, 37), (64, 16, 19, None), (256, 32, 16, 100)])
+@pytest.mark.parametrize("rank,rot,heads,window", [(160, 32, 5, 37), (64, 16, 19, None), (256, 32, 16, 100)])
 def test_tensor_core_latent_attention_against_the_cuda_core_kernel(rank, rot, heads, window):
     """Scattered pages, prompt portions beside single tokens, windows that end inside a tile of keys; one
     query and key scaled so that a single far key just inside the window carries its row."""
