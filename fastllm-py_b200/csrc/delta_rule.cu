@@ -120,7 +120,7 @@ __device__ __forceinline__ void delta_cp4(float* smem, const float* gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem));
 }
 
-template <int DPT, int COLS>
+template <int DPT, int COLS, bool VEC>
 __global__ void __launch_bounds__(COLS * DELTA_PARTS) delta_scan_kernel(
     float* __restrict__ work, long work_ld, float* __restrict__ state, long state_stride,
     const int* __restrict__ req_start, const int* __restrict__ req_ctx, const int* __restrict__ req_qlen,
@@ -196,8 +196,9 @@ __global__ void __launch_bounds__(COLS * DELTA_PARTS) delta_scan_kernel(
     float S[DPT];
     const bool fresh = req_ctx[r] == 0;
     fetch(0, 0);
-    // every thread's elements exist and every column starts on 16 bytes: four at a time
-    const bool whole = dim == DELTA_PARTS * DPT && state_stride % 4 == 0;
+    // VEC (steps of single tokens, where reading and writing the state is all the work): every thread's elements
+    // exist and every column starts on 16 bytes, so the state moves four floats at a time
+    const bool whole = VEC && dim == DELTA_PARTS * DPT && state_stride % 4 == 0;
     if (whole && !fresh) {
 #pragma unroll
         for (int i = 0; i < DPT; i += 4) {
@@ -315,11 +316,12 @@ FL_API int fl_delta_prep(const void* proj, int dtype, long ld, const void* conv_
     return 0;
 }
 
+// single_tokens: every request of the step brings one token (the state then moves in 16-byte pieces).
 // work: [n_tokens, work_ld] floats, a row = q | k (kv_heads x dim each) | v (heads x vdim) | beta | decay (heads
 // each) | o (heads x vdim): fl_delta_prep fills all but o, fl_delta_scan reads them and fills o.
 FL_API int fl_delta_scan(float* work, long work_ld, float* state, long state_stride,
                          const int* req_start, const int* req_ctx, const int* req_qlen, const int* req_slot,
-                         int n_requests, int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
+                         int n_requests, int heads, int kv_heads, int dim, int vdim, int single_tokens, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (heads % kv_heads || dim < 1 || dim > 32 * DELTA_PARTS) return (int)cudaErrorInvalidValue;
     const int per_thread = (dim + DELTA_PARTS - 1) / DELTA_PARTS;
@@ -329,21 +331,22 @@ FL_API int fl_delta_scan(float* work, long work_ld, float* state, long state_str
     const int cols = narrow ? 16 : DELTA_COLS;
     dim3 grid(n_requests * heads, (vdim + cols - 1) / cols);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
-#define FL_DELTA_SCAN_COLS(DPT, COLS)                                                                               \
+#define FL_DELTA_SCAN_COLS(DPT, COLS, VEC)                                                                          \
     {                                                                                                               \
         const size_t smem = (size_t)2 * DELTA_CHUNK * (2 * DELTA_PARTS * (DPT + 4) + COLS + 4) * sizeof(float);     \
         static bool raised = false;                                                                                 \
         if (smem > 48 * 1024 && !raised) {                                                                          \
-            const cudaError_t rc = cudaFuncSetAttribute(delta_scan_kernel<DPT, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            const cudaError_t rc = cudaFuncSetAttribute(delta_scan_kernel<DPT, COLS, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (rc != cudaSuccess) return (int)rc;                                                                  \
             raised = true;                                                                                          \
         }                                                                                                           \
-        return fl_launch(delta_scan_kernel<DPT, COLS>, grid, dim3(COLS * DELTA_PARTS), smem, stream, work, work_ld, state, \
+        return fl_launch(delta_scan_kernel<DPT, COLS, VEC>, grid, dim3(COLS * DELTA_PARTS), smem, stream, work, work_ld, state, \
                          state_stride, req_start, req_ctx, req_qlen, req_slot, heads, kv_heads, dim, vdim);         \
     }
 #define FL_DELTA_SCAN(DPT)                                                                                          \
     if (per_thread <= DPT) {                                                                                        \
-        if (narrow) FL_DELTA_SCAN_COLS(DPT, 16) else FL_DELTA_SCAN_COLS(DPT, 32)                                    \
+        if (single_tokens) { if (narrow) FL_DELTA_SCAN_COLS(DPT, 16, true) else FL_DELTA_SCAN_COLS(DPT, 32, true) }  \
+        else { if (narrow) FL_DELTA_SCAN_COLS(DPT, 16, false) else FL_DELTA_SCAN_COLS(DPT, 32, false) }             \
     }
     FL_DELTA_SCAN(4);
     FL_DELTA_SCAN(8);

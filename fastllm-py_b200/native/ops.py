@@ -309,10 +309,10 @@ def delta_scan(work, state, step, heads, kv_heads, dim, vdim):
     starts) and written; the o columns of `work` are filled."""
     _require_cuda(work, state)
     fn = _fn("delta_rule", "fl_delta_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p,
-                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(work), _ld(work), _ptr(state), state.stride(0), _ptr(step.req_start), _ptr(step.req_ctx),
               _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, kv_heads, dim, vdim,
-              _stream()), "delta_scan")
+              int(work.shape[0] == step.n_requests), _stream()), "delta_scan")
 
 
 def delta_gated_norm(work, o_col, proj, gate_col, weight, out, heads, vdim, eps):
