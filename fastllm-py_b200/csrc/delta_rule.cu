@@ -71,11 +71,13 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(
     for (int i = tid; i < count; i += blockDim.x) out_row[first + i] = conv_out[i];
     if (tid == 0) {
         const int h = unit - 2 * kv_heads;
-        const float b = to_f32<T>(row[channels + hv + h]);
-        const float a = to_f32<T>(row[channels + hv + heads + h]) + to_f32<TW>(dt_bias[h]);
-        const float softplus = a > 20.0f ? a : log1pf(expf(a));
-        out_row[channels + h] = 1.0f / (1.0f + expf(-b));
-        out_row[channels + heads + h] = expf(-expf(to_f32<TW>(a_log[h])) * softplus);
+        // two numbers a head and token, and the decay is multiplied up over thousands of tokens: formed in
+        // double and rounded once, so that no bias of a float exponential adds up along a sequence
+        const double b = (double)to_f32<T>(row[channels + hv + h]);
+        const double a = (double)to_f32<T>(row[channels + hv + heads + h]) + (double)to_f32<TW>(dt_bias[h]);
+        const double softplus = a > 30.0 ? a : log1p(exp(a));
+        out_row[channels + h] = (float)(1.0 / (1.0 + exp(-b)));
+        out_row[channels + heads + h] = (float)exp(-exp((double)to_f32<TW>(a_log[h])) * softplus);
     }
 }
 
