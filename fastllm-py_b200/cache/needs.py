@@ -72,3 +72,17 @@ class FixedState:
     request slot.  The mixer resets it when a request's first tokens arrive."""
     shape: tuple
     dtype: str = "float32"
+
+
+@dataclass(frozen=True)
+class PagedKeysValues(PagedNeed):
+    """Keys of `key_dim` and values of `value_dim` elements per token and head, the two sizes free of
+    one another (several key maps per head side by side, say): a page is
+    [kv_heads, page_size, key_dim + value_dim], a token's keys directly followed by its values."""
+    kv_heads: int
+    key_dim: int
+    value_dim: int
+    window: int | None = None
+
+    def page_shape(self, page_size: int) -> tuple:
+        return (self.kv_heads, page_size, self.key_dim + self.value_dim)

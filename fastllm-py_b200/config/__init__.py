@@ -2,11 +2,12 @@ from .base import ConfigError, read_raw_config
 from .engine import EngineConfig, canonical_dtype
 from .llama import LinearRopeScaling, LlamaConfig
 from .tigitar import TigitarConfig
+from .lasonex import LasonexConfig
 from .registry import (Architecture, architecture_names, architecture_of, load_config,
                        register_architecture)
 
 __all__ = [
     "ConfigError", "read_raw_config", "EngineConfig", "canonical_dtype", "LinearRopeScaling",
-    "LlamaConfig", "TigitarConfig", "Architecture", "architecture_names", "architecture_of", "load_config",
+    "LlamaConfig", "TigitarConfig", "LasonexConfig", "Architecture", "architecture_names", "architecture_of", "load_config",
     "register_architecture",
 ]

@@ -29,15 +29,15 @@ static inline bool vec4_ok(int dim, const void* base, long ld, size_t elem) {
 }
 
 // ------------------------------------------------------------------ embedding
-// out[t, :] = table[ids[t], :] as float (the residual stream is float in both
-// precisions).  An id outside [0, vocab) writes zeros and records 1 + t in
+// out[t, :] = table[ids[t], :] * scale as float (the residual stream is float in
+// both precisions; the product is formed in float).  An id outside [0, vocab) writes zeros and records 1 + t in
 // *status; it never reads outside the table.  A negative id -1 - r, when `fed`
 // is given, stands for fed[r]: a token that an earlier kernel of the stream
 // chose (the sampler's output row r) and the host has not read yet.
 template <typename TT>
 __global__ void embed_kernel(const TT* __restrict__ table, long table_ld, const int* __restrict__ ids,
                              float* __restrict__ out, long out_ld, int hidden, int vocab,
-                             int* __restrict__ status, int vec_ok, const int* __restrict__ fed, int n_fed) {
+                             int* __restrict__ status, int vec_ok, const int* __restrict__ fed, int n_fed, float scale) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
@@ -54,21 +54,22 @@ __global__ void embed_kernel(const TT* __restrict__ table, long table_ld, const 
         for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
             float4 v;
             load4(row + i, v);
+            v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
             *reinterpret_cast<float4*>(o + i) = v;
         }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<TT>(row[i]);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<TT>(row[i]) * scale;
     }
 }
 
 FL_API int fl_embed(const void* table, int table_dtype, long table_ld, const int* ids, float* out,
                     long out_ld, int n_tokens, int hidden, int vocab, int* status, const int* fed, int n_fed,
-                    cudaStream_t stream) {
+                    float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int vec = vec4_ok(hidden, table, table_ld, table_dtype == FL_F32 ? 4 : 2) && vec4_ok(hidden, out, out_ld, 4);
     FL_DISPATCH(table_dtype, TT,
                 return fl_launch(embed_kernel<TT>, dim3(n_tokens), dim3(256), 0, stream, (const TT*)table,
-                                 table_ld, ids, out, out_ld, hidden, vocab, status, vec, fed, n_fed));
+                                 table_ld, ids, out, out_ld, hidden, vocab, status, vec, fed, n_fed, scale));
     return 0;
 }
 
@@ -452,31 +453,23 @@ FL_API int fl_swiglu_partial(const float* partial, int splits, long split_stride
 
 // ------------------------------------------------- gated linear unit, any activation
 // out[r, i] = act(gu[r, i]) * gu[r, inter + i].  act: 0 silu, 1 relu, 2 gelu (tanh form).
-enum FlAct : int { FL_ACT_SILU = 0, FL_ACT_RELU = 1, FL_ACT_GELU_TANH = 2 };
-
-__device__ __forceinline__ float fl_act(float g, int act) {
-    if (act == FL_ACT_RELU) return fmaxf(g, 0.0f);
-    if (act == FL_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-    return g / (1.0f + expf(-g));
-}
-
 template <typename T>
-__global__ void glu_kernel(const T* __restrict__ gu, long gu_ld, T* __restrict__ out, long out_ld, int inter, int act) {
+__global__ void glu_kernel(const T* __restrict__ gu, long gu_ld, T* __restrict__ out, long out_ld, int inter, FlGate act) {
     pdl_wait();
     pdl_trigger();
     const T* g = gu + (long)blockIdx.y * gu_ld;
     T* o = out + (long)blockIdx.y * out_ld;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < inter) o[i] = from_f32<T>(fl_act(to_f32<T>(g[i]), act) * to_f32<T>(g[inter + i]));
+    if (i < inter) o[i] = from_f32<T>(fl_gated(to_f32<T>(g[i]), to_f32<T>(g[inter + i]), act));
 }
 
 FL_API int fl_glu(const void* gu, int dtype, long gu_ld, void* out, long out_ld, int n_rows, int inter, int act,
-                  cudaStream_t stream) {
+                  float act_p0, float act_p1, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (n_rows > 65535 || act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+    if (n_rows > 65535 || act < 0 || act >= FL_ACT_COUNT) return (int)cudaErrorInvalidValue;
     dim3 grid((inter + 255) / 256, n_rows);
     FL_DISPATCH(dtype, T, return fl_launch(glu_kernel<T>, grid, dim3(256), 0, stream, (const T*)gu, gu_ld, (T*)out,
-                                           out_ld, inter, act));
+                                           out_ld, inter, FlGate{act, act_p0, act_p1}));
     return 0;
 }
 
@@ -600,5 +593,54 @@ FL_API int fl_sandwich_norm_partial(float* x, long x_ld, const float* partial, i
         return fl_launch(sandwich_norm_partial_kernel<TW, TO>, dim3(n_rows), dim3(threads), (size_t)dim * sizeof(float),
                          stream, x, x_ld, partial, splits, split_stride, ld, (const TW*)w_post, eps_post,
                          (const TW*)w_pre, eps_pre, (TO*)out, out_ld, dim)));
+    return 0;
+}
+
+// ------------------------------------------------- two sums pending, two norms of one row
+// A layer whose mixer and feed-forward both read the same x leaves two outputs to add, and the
+// next such layer norms the sum twice, with two weights but one root mean square:
+//     x += d1 + d2;   r = (mean(x^2) + eps)^-1/2;   out1 = x r w1;   out2 = x r w2
+// d1, d2, w2 / out2 may each be absent.  x is the float residual stream (written back unless rows
+// are gathered).  The summed row waits in shared memory between the reduction and the last pass.
+template <typename TD, typename TW, typename TO>
+__global__ void norm_pair_kernel(float* __restrict__ x, long x_ld, const TD* __restrict__ d1, long d1_ld,
+                                 const TD* __restrict__ d2, long d2_ld, const TW* __restrict__ w1,
+                                 const TW* __restrict__ w2, TO* __restrict__ out1, long out1_ld, TO* __restrict__ out2,
+                                 long out2_ld, int dim, float eps, const int* __restrict__ rows) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float pair_row[];                     // [dim]
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long src = rows ? (long)rows[r] : (long)r;
+    float* xr = x + src * x_ld;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = xr[i];
+        if (d1) v += to_f32<TD>(d1[src * d1_ld + i]);
+        if (d2) v += to_f32<TD>(d2[src * d2_ld + i]);
+        if ((d1 || d2) && !rows) xr[i] = v;
+        pair_row[i] = v;                                    // each thread re-reads what it wrote itself
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = pair_row[i] * inv;
+        out1[(long)r * out1_ld + i] = from_f32<TO>(v * to_f32<TW>(w1[i]));
+        if (out2) out2[(long)r * out2_ld + i] = from_f32<TO>(v * to_f32<TW>(w2[i]));
+    }
+}
+
+FL_API int fl_norm_pair(float* x, long x_ld, const void* d1, long d1_ld, const void* d2, long d2_ld, int d_dtype,
+                        const void* w1, const void* w2, int w_dtype, void* out1, long out1_ld, void* out2, long out2_ld,
+                        int out_dtype, int n_rows, int dim, float eps, const int* rows, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if ((size_t)dim * sizeof(float) > 48 * 1024 || (out2 != nullptr) != (w2 != nullptr)) return (int)cudaErrorInvalidValue;
+    const int threads = norm_threads(dim, false);
+    FL_DISPATCH(d_dtype, TD, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
+        return fl_launch(norm_pair_kernel<TD, TW, TO>, dim3(n_rows), dim3(threads), (size_t)dim * sizeof(float), stream,
+                         x, x_ld, (const TD*)d1, d1_ld, (const TD*)d2, d2_ld, (const TW*)w1, (const TW*)w2, (TO*)out1,
+                         out1_ld, (TO*)out2, out2_ld, dim, eps, rows))));
     return 0;
 }

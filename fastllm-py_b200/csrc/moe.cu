@@ -4,7 +4,10 @@
 //   moe_pick      per token, from the router's float logits z (a product the caller makes): score
 //                 s = sigmoid(z) (or a softmax over the experts); the `top` experts with the largest
 //                 s + bias are chosen (the bias steers the choice only), ties to the lower index; the
-//                 weights are the chosen s, optionally renormalised to sum 1
+//                 weights are the chosen s, optionally renormalised to sum 1 (divided by their sum + an
+//                 epsilon).  With groups, the experts form `n_groups` equal groups of neighbours, a
+//                 group's score is the largest s + bias in it, and only experts of the `keep` best
+//                 groups (ties to the lower index) can be chosen
 //   moe_gate_up   per (token, choice): act(W_gate[e] h) * (W_up[e] h), one warp per feature
 //   moe_down      per token: sum over its choices, in order of choice, of weight * W_down[e] a
 //
@@ -13,24 +16,19 @@
 // on the token itself.
 #include "common.cuh"
 
-__device__ __forceinline__ float moe_act(float g, int act) {
-    if (act == 1) return fmaxf(g, 0.0f);
-    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-    return g / (1.0f + expf(-g));
-}
-
 // One warp per token; z: float logits [n_tokens, experts] (the router's product, made by the caller).
 template <typename TW>
 __global__ void __launch_bounds__(128) moe_pick_kernel(const float* __restrict__ z, long z_ld, const TW* __restrict__ bias,
                                                        int* __restrict__ chosen, float* __restrict__ weights, int n_tokens,
-                                                       int experts, int top, int softmax_scores, int renormalise) {
+                                                       int experts, int top, int softmax_scores, int renormalise,
+                                                       int n_groups, int keep, float renorm_eps) {
     pdl_wait();
     pdl_trigger();
-    extern __shared__ float route_s[];                  // per warp: [experts] scores, [experts] scores + bias
+    extern __shared__ float route_s[];                  // per warp: [experts] scores, [experts] scores + bias, [n_groups]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     if (t >= n_tokens) return;
-    float* score = route_s + (long)warp * 2 * experts;
+    float* score = route_s + (long)warp * (2 * experts + n_groups);
     float* pick = score + experts;
     const float* zr = z + (long)t * z_ld;
     if (softmax_scores) {
@@ -46,6 +44,24 @@ __global__ void __launch_bounds__(128) moe_pick_kernel(const float* __restrict__
     }
     for (int e = lane; e < experts; e += 32) pick[e] = score[e] + (bias ? to_f32<TW>(bias[e]) : 0.0f);
     __syncwarp();
+    if (n_groups > 1 && keep < n_groups) {
+        const int per = experts / n_groups;
+        float* group = pick + experts;
+        for (int g = lane; g < n_groups; g += 32) {
+            float b = -CUDART_INF_F;
+            for (int i = 0; i < per; ++i) b = fmaxf(b, pick[g * per + i]);
+            group[g] = b;
+        }
+        __syncwarp();
+        for (int g = lane; g < n_groups; g += 32) {
+            const float mine = group[g];
+            int ahead = 0;                              // groups that come before this one
+            for (int o = 0; o < n_groups; ++o) ahead += (group[o] > mine) || (group[o] == mine && o < g);
+            if (ahead >= keep)
+                for (int i = 0; i < per; ++i) pick[g * per + i] = -CUDART_INF_F;
+        }
+        __syncwarp();
+    }
     float total = 0.0f;
     for (int k = 0; k < top; ++k) {
         float best = -CUDART_INF_F;
@@ -67,14 +83,14 @@ __global__ void __launch_bounds__(128) moe_pick_kernel(const float* __restrict__
         __syncwarp();
     }
     if (renormalise && lane == 0)
-        for (int k = 0; k < top; ++k) weights[(long)t * top + k] /= total;
+        for (int k = 0; k < top; ++k) weights[(long)t * top + k] /= total + renorm_eps;
 }
 
 // w_gu: [experts][2 ff][width] (gate rows, then up rows); a: [tokens x top][ff] float
 template <typename T, typename TW>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ h, long h_ld, const TW* __restrict__ w_gu,
                                                           const int* __restrict__ chosen, float* __restrict__ a,
-                                                          int width, int ff, int top, int act) {
+                                                          int width, int ff, int top, FlGate act) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float moe_x[];                    // [width]
@@ -93,7 +109,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ 
     }
     g = warp_sum(g);
     u = warp_sum(u);
-    if (lane == 0) a[(long)pair * ff + f] = moe_act(g, act) * u;
+    if (lane == 0) a[(long)pair * ff + f] = fl_gated(g, u, act);
 }
 
 // w_down: [experts][width][ff]
@@ -119,26 +135,32 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const float* __restrict__
 }
 
 FL_API int fl_moe_pick(const float* z, long z_ld, const void* bias, int bias_dtype, int* chosen, float* weights,
-                       int n_tokens, int experts, int top, int softmax_scores, int renormalise, cudaStream_t stream) {
+                       int n_tokens, int experts, int top, int softmax_scores, int renormalise, int n_groups, int keep,
+                       float renorm_eps, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (top < 1 || top > experts || (size_t)experts * 8 * 4 > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (n_groups < 1) n_groups = keep = 1;
+    const size_t smem = (size_t)(2 * experts + n_groups) * 4 * sizeof(float);
+    if (top < 1 || top > experts || smem > 48 * 1024 || experts % n_groups || keep < 1 || keep > n_groups ||
+        (long)keep * (experts / n_groups) < top)
+        return (int)cudaErrorInvalidValue;
     FL_DISPATCH(bias_dtype, TW,
-        return fl_launch(moe_pick_kernel<TW>, dim3((n_tokens + 3) / 4), dim3(128), (size_t)experts * 8 * sizeof(float), stream,
-                         z, z_ld, (const TW*)bias, chosen, weights, n_tokens, experts, top, softmax_scores, renormalise));
+        return fl_launch(moe_pick_kernel<TW>, dim3((n_tokens + 3) / 4), dim3(128), smem, stream,
+                         z, z_ld, (const TW*)bias, chosen, weights, n_tokens, experts, top, softmax_scores, renormalise,
+                         n_groups, keep, renorm_eps));
     return 0;
 }
 
 FL_API int fl_moe_experts(const void* h, int dtype, long h_ld, const void* w_gu, const void* w_down, int w_dtype,
                           const int* chosen, const float* weights, float* a, void* out, long out_ld, int n_tokens,
-                          int width, int ff, int top, int act, cudaStream_t stream) {
+                          int width, int ff, int top, int act, float act_p0, float act_p1, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if ((size_t)width * sizeof(float) > 48 * 1024 || (ff + 7) / 8 > 65535 || (width + 7) / 8 > 65535 || act < 0 || act > 2)
+    if ((size_t)width * sizeof(float) > 48 * 1024 || (ff + 7) / 8 > 65535 || (width + 7) / 8 > 65535 || act < 0 || act >= FL_ACT_COUNT)
         return (int)cudaErrorInvalidValue;
     int rc = 0;
     FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
         rc = fl_launch(moe_gate_up_kernel<T, TW>, dim3(n_tokens * top, (ff + 7) / 8), dim3(256),
                        (size_t)width * sizeof(float), stream, (const T*)h, h_ld, (const TW*)w_gu, chosen, a, width, ff,
-                       top, act)));
+                       top, FlGate{act, act_p0, act_p1})));
     if (rc) return rc;
     FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
         return fl_launch(moe_down_kernel<T, TW>, dim3(n_tokens, (width + 7) / 8), dim3(256), 0, stream, (const float*)a,
@@ -218,7 +240,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(256) moe_group_mma_kernel(
     const bf16* __restrict__ a, long a_ld, const bf16* __restrict__ w, int n_out, int K, const int* __restrict__ row_pair,
     const int* __restrict__ tile_expert, const int* __restrict__ n_tiles, int top, bf16* __restrict__ act_out,
-    float* __restrict__ y_out, long out_ld, int act) {
+    float* __restrict__ y_out, long out_ld, FlGate act) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ __align__(16) unsigned char moe_smem[];
@@ -324,8 +346,8 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
                     for (int c = 0; c < 2; ++c) {
                         const int f = blockIdx.y * 64 + wn * 16 + j * 8 + (lane & 3) * 2 + c;
                         if (f < n_out)
-                            act_out[row * out_ld + f] = __float2bfloat16_rn(moe_act(acc[i][j][half * 2 + c], act) *
-                                                                            acc[i][j + 2][half * 2 + c]);
+                            act_out[row * out_ld + f] = __float2bfloat16_rn(fl_gated(acc[i][j][half * 2 + c],
+                                                                                     acc[i][j + 2][half * 2 + c], act));
                     }
             } else {
 #pragma unroll
@@ -377,8 +399,11 @@ static int moe_group_smem_ready() {
 // act: bfloat16 [rows, ff]; y: float [rows, width].
 FL_API int fl_moe_experts_grouped(const void* h, long h_ld, const void* w_gu, const void* w_down, const int* chosen,
                                   const float* weights, int* ints, void* act, float* y, void* out, long out_ld,
-                                  int n_tokens, int width, int ff, int top, int experts, int act_code, cudaStream_t stream) {
+                                  int n_tokens, int width, int ff, int top, int experts, int act_code, float act_p0, float act_p1,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (act_code < 0 || act_code >= FL_ACT_COUNT) return (int)cudaErrorInvalidValue;
+    const FlGate gate{act_code, act_p0, act_p1};
     const long rows = fl_moe_group_rows(n_tokens, top, experts);
     const int max_tiles = (int)(rows / MOE_TM);
     int* row_pair = ints;
@@ -393,11 +418,11 @@ FL_API int fl_moe_experts_grouped(const void* h, long h_ld, const void* w_gu, co
     if (rc) return rc;
     rc = fl_launch(moe_group_mma_kernel<true>, dim3(max_tiles, (ff + 63) / 64), dim3(256), MOE_SMEM, stream, (const bf16*)h, h_ld,
                    (const bf16*)w_gu, ff, width, (const int*)row_pair, (const int*)tile_expert, (const int*)n_tiles, top,
-                   (bf16*)act, (float*)nullptr, (long)ff, act_code);
+                   (bf16*)act, (float*)nullptr, (long)ff, gate);
     if (rc) return rc;
     rc = fl_launch(moe_group_mma_kernel<false>, dim3(max_tiles, (width + 127) / 128), dim3(256), MOE_SMEM, stream,
                    (const bf16*)act, (long)ff, (const bf16*)w_down, width, ff, (const int*)row_pair,
-                   (const int*)tile_expert, (const int*)n_tiles, top, (bf16*)nullptr, y, (long)width, act_code);
+                   (const int*)tile_expert, (const int*)n_tiles, top, (bf16*)nullptr, y, (long)width, gate);
     if (rc) return rc;
     int col_blocks = (width + 255) / 256;
     if (col_blocks > 8) col_blocks = 8;

@@ -252,10 +252,12 @@ def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
     return partial
 
 
-def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor, activation: str = "silu") -> bool:
+def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor, activation: str = "silu", params=(0.0, 0.0)) -> bool:
     """out[M, I] = act(a @ gate^T) * (a @ up^T) for w = [gate; up] stacked as [2 I, K], all
     bfloat16, in one kernel (the activation in the product's epilogue; silu, relu or gelu_tanh).
     Returns False, having done nothing, when the kernel does not take the problem (its plan splits K)."""
+    if ops.activation_code(activation) > 2:                 # units with constants of their own: product, then ops.glu
+        return False
     key = ("glu", activation, a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, out.data_ptr(), out.shape,
            out.stride(0), out.dtype)
     known = _launches.get(key)                              # (see gemm)

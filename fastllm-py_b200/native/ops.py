@@ -106,17 +106,17 @@ def _fn(lib_name: str, fn_name: str, argtypes, defines=None):
 
 # ---------------------------------------------------------------- elementwise
 
-def embed(table, ids, out, status, fed=None):
-    """out[t] = table[ids[t]] as float32; an id outside the table sets status[0] = t + 1.
+def embed(table, ids, out, status, fed=None, scale=1.0):
+    """out[t] = table[ids[t]] * scale as float32; an id outside the table sets status[0] = t + 1.
     With `fed` (int32 on the device), an id -1 - r is replaced by fed[r]."""
     _require_cuda(table, ids, out, status, fed)
     fn = _fn("elementwise", "fl_embed", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_long, c_int,
-                                         c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+                                         c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p])
     if out.dtype != torch.float32 or ids.dtype != torch.int32 or (fed is not None and fed.dtype != torch.int32):
         raise KernelError("embed: out must be float32, ids (and fed) int32")
     _check(fn(_ptr(table), dtype_code(table), _ld(table), _ptr(ids), _ptr(out), _ld(out),
               ids.numel(), table.shape[1], table.shape[0], _ptr(status), _ptr(fed),
-              0 if fed is None else fed.numel(), _stream()), "embed")
+              0 if fed is None else fed.numel(), float(scale), _stream()), "embed")
 
 
 def rmsnorm(x, weight, out, eps, rows=None):
@@ -221,17 +221,21 @@ def swiglu(gate_up, out):
               out.shape[1], _stream()), "swiglu")
 
 
-def glu(gate_up, out, activation: str = "silu"):
-    """out[:, i] = act(gate_up[:, i]) * gate_up[:, I + i], I = out.shape[1]; act: silu, relu, gelu_tanh."""
+def glu(gate_up, out, activation: str = "silu", params=(0.0, 0.0)):
+    """out[:, i] = f(gate_up[:, i], gate_up[:, I + i]), I = out.shape[1]; f: see ACTIVATIONS."""
     _require_cuda(gate_up, out)
     if gate_up.dtype != out.dtype:
         raise KernelError("glu: input and output must have one dtype")
-    fn = _fn("elementwise", "fl_glu", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p])
+    fn = _fn("elementwise", "fl_glu", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_float, c_float,
+                                       c_void_p])
     _check(fn(_ptr(gate_up), dtype_code(gate_up), _ld(gate_up), _ptr(out), _ld(out), out.shape[0],
-              out.shape[1], activation_code(activation), _stream()), "glu")
+              out.shape[1], activation_code(activation), float(params[0]), float(params[1]), _stream()), "glu")
 
 
-ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+# Gated units f(g, u) of a gate value and an up value.  silu, relu, gelu_tanh: act(g) * u.
+# clamped_swish with params (limit, slope): g' = min(g, limit), u' = clamp(u, -limit, limit),
+# f = g' * sigmoid(slope * g') * (u' + 1).
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "clamped_swish": 3}
 
 
 def activation_code(name: str) -> int:
@@ -279,6 +283,99 @@ def softcap(logits, cap: float):
         raise KernelError("softcap: logits must be float32")
     fn = _fn("elementwise", "fl_softcap", [c_void_p, c_long, c_int, c_int, c_float, c_void_p])
     _check(fn(_ptr(logits), _ld(logits), logits.shape[0], logits.shape[1], float(cap), _stream()), "softcap")
+
+
+def norm_pair(resid, d1, d2, w1, w2, out1, out2, eps, rows=None):
+    """resid += d1 + d2 (each may be None; written back unless rows are gathered); r = rms of the row;
+    out1 = resid / r * w1 and, when given, out2 = resid / r * w2: two norms of one row in one pass."""
+    _require_cuda(resid, d1, d2, w1, w2, out1, out2, rows)
+    if resid.dtype != torch.float32:
+        raise KernelError("norm_pair: the residual stream must be float32")
+    if (d1 is not None and d2 is not None and d1.dtype != d2.dtype) or (w2 is not None and w2.dtype != w1.dtype) or \
+            (out2 is not None and out2.dtype != out1.dtype) or (w2 is None) != (out2 is None):
+        raise KernelError("norm_pair: both sums, both weights and both outputs share a dtype each")
+    fn = _fn("elementwise", "fl_norm_pair", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p,
+                                             c_void_p, c_int, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                             c_float, c_void_p, c_void_p])
+    d = d1 if d1 is not None else d2
+    _check(fn(_ptr(resid), _ld(resid), _ptr(d1), 0 if d1 is None else _ld(d1), _ptr(d2), 0 if d2 is None else _ld(d2),
+              F32 if d is None else dtype_code(d), _ptr(w1), _ptr(w2), dtype_code(w1), _ptr(out1), _ld(out1),
+              _ptr(out2), 0 if out2 is None else _ld(out2), dtype_code(out1), out1.shape[0], resid.shape[1],
+              float(eps), _ptr(rows), _stream()), "norm_pair")
+
+
+# ------------------------------------------------------ differential attention
+
+def diff_prep(proj, heads, kv_heads, dim, vdim, rot, cos, sin, positions, slots, cache, page_size):
+    """proj columns q (heads x 2 maps x dim) | k (kv_heads x 2 x dim) | v (kv_heads x vdim): rotates the first `rot`
+    dimensions of every query map in place (pairs (i, i + rot/2)); rotates the key maps into each token's cache
+    row and copies its value behind them.  `cache`: one layer's [pages, kv_heads, page_size, 2 dim + vdim]."""
+    _require_cuda(proj, cos, sin, positions, slots, cache)
+    if cache is not None and (cache.dtype != proj.dtype or not cache.is_contiguous()):
+        raise KernelError("diff_prep: the cache must be contiguous and of the activations' dtype")
+    fn = _fn("diff_attention", "fl_diff_prep", [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int,
+                                                c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), proj.shape[0], heads, kv_heads, dim, vdim, rot, _ptr(cos),
+              _ptr(sin), _ptr(positions), _ptr(slots), _ptr(cache), 0 if cache is None else cache.stride(0), page_size,
+              _stream()), "diff_prep")
+
+
+def diff_attention_simt(q, out, cache, block_table, tok_req, positions, heads, kv_heads, dim, vdim, window, scale,
+                        lam, eps, out_scale, page_size):
+    """Differential attention of every token over its request's cache rows on CUDA cores: per head
+    o = softmax-map 1 - lam * softmax-map 2 (both over the same values), out = o / rms(o) * out_scale."""
+    _require_cuda(q, out, cache, block_table, tok_req, positions)
+    if q.dtype != cache.dtype or out.dtype != q.dtype:
+        raise KernelError("diff_attention: q, cache and out share a dtype")
+    fn = _fn("diff_attention", "fl_diff_attention_simt",
+             [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_void_p])
+    _check(fn(_ptr(q), dtype_code(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size,
+              _ptr(block_table), block_table.stride(0), _ptr(tok_req), _ptr(positions), q.shape[0], heads, kv_heads,
+              dim, vdim, int(window or 0), float(scale), float(lam), float(eps), float(out_scale), _stream()),
+           "diff_attention_simt")
+
+
+# ------------------------------------------------------------------ retention
+
+def retention_prep(proj, work, heads, dim, rot, cos, sin, positions, k_scale):
+    """proj columns q (heads x dim) | k (heads x dim) | ...: rotated (pairs (i, i + rot/2) of the first `rot`
+    dimensions), k times `k_scale`, into the float32 columns q | k of `work`."""
+    _require_cuda(proj, work, cos, sin, positions)
+    if work.dtype != torch.float32:
+        raise KernelError("retention_prep: the work buffer must be float32")
+    fn = _fn("retention", "fl_retention_prep", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int,
+                                                c_void_p, c_void_p, c_void_p, c_float, c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(work), _ld(work), proj.shape[0], heads, dim, rot, _ptr(cos),
+              _ptr(sin), _ptr(positions), float(k_scale), _stream()), "retention_prep")
+
+
+def retention_scan(work, proj, v_col, o, state, decay, step, heads, dim, vdim):
+    """Per request and head S <- decay S + k v^T, o = S^T q over the step's tokens; q | k are the float32 columns of
+    `work`, v the columns of `proj` from `v_col` on, `o` float32 [N, heads * vdim]; state rows [heads, vdim, dim]
+    float32 are read (unless the request starts) and written."""
+    _require_cuda(work, proj, o, state, decay)
+    if work.dtype != torch.float32 or o.dtype != torch.float32 or state.dtype != torch.float32 or \
+            decay.dtype != torch.float32:
+        raise KernelError("retention_scan: work, o, state and decay must be float32")
+    fn = _fn("retention", "fl_retention_scan", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_long, c_void_p,
+                                                c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                c_int, c_int, c_void_p])
+    _check(fn(_ptr(work), _ld(work), c_void_p(proj.data_ptr() + proj.element_size() * v_col), dtype_code(proj), _ld(proj),
+              _ptr(o), _ld(o), _ptr(state), state.stride(0), _ptr(decay), _ptr(step.req_start), _ptr(step.req_ctx),
+              _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, dim, vdim, _stream()), "retention_scan")
+
+
+def retention_gated_norm(o, proj, gate_col, out, heads, vdim, eps):
+    """out[t, h] = o[t, h] / rms(o[t, h]) * silu(gate[t, h]); gate are the columns of `proj` from `gate_col` on."""
+    _require_cuda(o, proj, out)
+    if proj.dtype != out.dtype or o.dtype != torch.float32:
+        raise KernelError("retention_gated_norm: gate and out share a dtype, o is float32")
+    fn = _fn("retention", "fl_retention_gated_norm", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_long, c_int,
+                                                      c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(o), _ld(o), c_void_p(proj.data_ptr() + proj.element_size() * gate_col), dtype_code(proj), _ld(proj),
+              _ptr(out), _ld(out), out.shape[0], heads, vdim, float(eps), _stream()), "retention_gated_norm")
 
 
 # ---------------------------------------------------------------- delta rule
@@ -419,29 +516,33 @@ def gemm_batched(a, a_batch, w, out, out_batch):
 
 # ------------------------------------------------------------- routed experts
 
-def moe_pick(logits, bias, chosen, weights, top, softmax_scores=False, renormalise=False):
+def moe_pick(logits, bias, chosen, weights, top, softmax_scores=False, renormalise=False, groups=None, keep=None,
+             renormalise_eps=0.0):
     """Per token, from the router's float32 logits [N, experts]: the `top` experts by score + bias (int32
-    `chosen` [N, top]) and their scores (`weights`); scores are sigmoids, or a softmax over the experts."""
+    `chosen` [N, top]) and their scores (`weights`, divided by their sum + `renormalise_eps` with
+    `renormalise`); scores are sigmoids, or a softmax over the experts.  With `groups` the experts form that
+    many equal groups of neighbours and only those of the `keep` groups with the largest best score + bias
+    can be chosen."""
     _require_cuda(logits, bias, chosen, weights)
     if logits.dtype != torch.float32 or chosen.shape[1] != top or not chosen.is_contiguous() or not weights.is_contiguous():
         raise KernelError("moe_pick: logits float32, chosen and weights contiguous [N, top]")
     fn = _fn("moe", "fl_moe_pick", [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                    c_int, c_void_p])
+                                    c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(_ptr(logits), _ld(logits), _ptr(bias), F32 if bias is None else dtype_code(bias), _ptr(chosen),
-              _ptr(weights), logits.shape[0], logits.shape[1], top, int(softmax_scores), int(renormalise), _stream()),
-           "moe_pick")
+              _ptr(weights), logits.shape[0], logits.shape[1], top, int(softmax_scores), int(renormalise),
+              int(groups or 1), int(keep or groups or 1), float(renormalise_eps), _stream()), "moe_pick")
 
 
-def moe_experts(h, w_gate_up, w_down, chosen, weights, act_buf, out, activation="silu"):
-    """out[t] = sum_k weights[t, k] * down[e](act(gate[e] h[t]) * (up[e] h[t])), e = chosen[t, k];
+def moe_experts(h, w_gate_up, w_down, chosen, weights, act_buf, out, activation="silu", params=(0.0, 0.0)):
+    """out[t] = sum_k weights[t, k] * down[e](f(gate[e] h[t], up[e] h[t])), e = chosen[t, k], f as in ACTIVATIONS;
     w_gate_up [E, 2 ff, width], w_down [E, width, ff]; act_buf float32 [N * top, ff]."""
     _require_cuda(h, w_gate_up, w_down, chosen, weights, act_buf, out)
     experts, ff2, width = w_gate_up.shape
     fn = _fn("moe", "fl_moe_experts", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                       c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                                       c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(fn(_ptr(h), dtype_code(h), _ld(h), _ptr(w_gate_up), _ptr(w_down), dtype_code(w_gate_up), _ptr(chosen),
               _ptr(weights), _ptr(act_buf), _ptr(out), _ld(out), h.shape[0], width, ff2 // 2, chosen.shape[1],
-              activation_code(activation), _stream()), "moe_experts", 2)
+              activation_code(activation), float(params[0]), float(params[1]), _stream()), "moe_experts", 2)
 
 
 def moe_group_rows(n_tokens: int, top: int, experts: int) -> int:
@@ -460,7 +561,7 @@ def moe_group_takes(h_dtype, w_dtype, width: int, ff: int) -> bool:
     return bool(fn(_CODES[h_dtype], _CODES[w_dtype], width, ff))
 
 
-def moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, ints, act, y, out, activation="silu"):
+def moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, ints, act, y, out, activation="silu", params=(0.0, 0.0)):
     """The same sum as `moe_experts` for many tokens: pairs ordered by expert, two tensor-core products
     over tiles of 64 rows, then the weighted sum per token.  All bfloat16; `ints` int32
     [rows + N * top + rows / 64 + 1], `act` bfloat16 [rows, ff], `y` float32 [rows, width] with
@@ -469,10 +570,10 @@ def moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, ints, act, y, out
     experts, ff2, width = w_gate_up.shape
     fn = _fn("moe", "fl_moe_experts_grouped", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
-                                               c_int, c_void_p])
+                                               c_int, c_float, c_float, c_void_p])
     _check(fn(_ptr(h), _ld(h), _ptr(w_gate_up), _ptr(w_down), _ptr(chosen), _ptr(weights), _ptr(ints), _ptr(act),
               _ptr(y), _ptr(out), _ld(out), h.shape[0], width, ff2 // 2, chosen.shape[1], experts,
-              activation_code(activation), _stream()), "moe_experts_grouped", 4)
+              activation_code(activation), float(params[0]), float(params[1]), _stream()), "moe_experts_grouped", 4)
 
 
 # -------------------------------------------------------------- rope + cache

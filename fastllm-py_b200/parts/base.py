@@ -33,6 +33,9 @@ What a part may declare beside its interface (all optional; absent means "no"):
                            (otherwise the stream adds them up into a tensor first)
   takes_post_norm = True   norm: `apply` understands `stream.pending_norm` (the pending sum is normed by
                            that part before it is added); such a norm also has `add_normed(stream)`
+  takes_extra = True       norm: `apply` adds `stream.extra` (a second tensor) along with a pending tensor; such a
+                           norm also has `apply_pair(stream, other, out, out_other)`: its own norm and that of
+                           `other` (same kind, size and eps) of the one row in one pass
   takes_fed_tokens = True  embedding: understands a token id -1 - r as "row r of `step.token_feed`"
                            (without it the scheduler never launches a step ahead of the host)
 """
@@ -101,6 +104,8 @@ class ResidualStream:
         self.pending = None
         self.pending_norm = None     # a norm part the pending sum passes before it is added (blocks that norm
         self.spill = spill           # a sublayer's output); a norm with `takes_post_norm` does both in one kernel
+        self.extra = None            # a second tensor not yet added (a layer whose mixer and feed-forward run side by
+                                     # side leaves two); a norm with `takes_extra` adds both while it reads
 
     def norm_into(self, norm, out, rows=None):
         """`norm.apply(self, out, rows)`, with a pending sum that the norm can take."""
@@ -112,6 +117,11 @@ class ResidualStream:
                 pending = self.pending = pending.reduce_into(self.spill())
         if pending is not None and self.pending_norm is not None and not getattr(norm, "takes_post_norm", False):
             self.pending_norm.add_normed(self)           # x += norm(pending), for a norm that cannot do it itself
+        if self.extra is not None and (not getattr(norm, "takes_extra", False) or self.pending_norm is not None
+                                       or not isinstance(self.pending, torch.Tensor)):
+            from ..native import ops
+            ops.residual_add(self.x, self.extra)         # x += extra, for a norm (or a pending sum) that cannot
+            self.extra = None
         norm.apply(self, out, rows)
 
 

@@ -8,8 +8,15 @@ The sums are left pending on the residual stream and folded into the next norm.
     x = x + norm_mixer_out(mixer(norm_mixer_in(x)));  x = x + norm_ff_out(ff(norm_ff_in(x)))
 and may have no feed-forward at all.  The sublayer's output is left pending with
 its norm; the next norm of the stream does norm, add and norm in one kernel.
+
+"parallel" runs mixer and feed-forward side by side on the same x, each behind a norm of its own:
+    x = x + mixer(norm_mixer(x)) + feed_forward(norm_ff(x))
+and may have no feed-forward.  Both outputs are left pending; the next layer's two norms share
+the row's root mean square, so one kernel adds both sums and writes both normed rows.
 """
 from __future__ import annotations
+
+import torch
 
 from .base import Part
 from .registry import build_part, register_part
@@ -81,3 +88,55 @@ class SandwichBlock(Part):
             stream.norm_into(self.norm_ff_in, h)
             left = self.feed_forward.forward(h, delta, step)
             stream.pending, stream.pending_norm = (delta if left is None else left), self.norm_ff_out
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Part):
+    """norm roles: "mixer" and, with a feed-forward, "feed_forward"."""
+    category = "block"
+
+    def __init__(self, layer_spec, ctx):
+        super().__init__(layer_spec, ctx)
+        self.mixer = build_part("mixer", layer_spec.mixer, ctx)
+        self.norm_mixer = build_part("norm", layer_spec.norms["mixer"], ctx)
+        self.feed_forward = self.norm_ff = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, ctx)
+            self.norm_ff = build_part("norm", layer_spec.norms["feed_forward"], ctx)
+        self.hidden = self.norm_mixer.size
+
+    def children(self):
+        parts = [self.mixer, self.norm_mixer]
+        if self.feed_forward is not None:
+            parts += [self.feed_forward, self.norm_ff]
+        return parts
+
+    def forward(self, stream, step, cache):
+        n = stream.x.shape[0]
+        dt = self.ctx.dtype
+        ws = step.workspace
+        h = ws.rows("normed", n, self.hidden, dt)
+        delta = ws.rows("delta", n, self.hidden, dt)
+        if self.feed_forward is None:
+            stream.norm_into(self.norm_mixer, h)
+        else:
+            h_ff = ws.rows("normed_ff", n, self.hidden, dt)
+            pairs = getattr(self.norm_mixer, "pairs_with", None)
+            if pairs is not None and pairs(self.norm_ff) and stream.pending_norm is None:
+                if stream.pending is not None and not isinstance(stream.pending, torch.Tensor):
+                    stream.pending = stream.pending.reduce_into(stream.spill())
+                self.norm_mixer.apply_pair(stream, self.norm_ff, h, h_ff)
+            else:
+                stream.norm_into(self.norm_mixer, h)          # adds what was pending
+                stream.norm_into(self.norm_ff, h_ff)
+        # the split-K scratch is shared: partial sums are added up before the other sublayer's products run
+        left = self.mixer.forward(h, delta, step, cache)
+        if left is not None:
+            left.reduce_into(delta)
+        stream.pending = delta
+        if self.feed_forward is not None:
+            delta_ff = ws.rows("delta_ff", n, self.hidden, dt)
+            left = self.feed_forward.forward(h_ff, delta_ff, step)
+            if left is not None:
+                left.reduce_into(delta_ff)
+            stream.extra = delta_ff

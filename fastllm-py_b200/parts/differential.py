@@ -1,0 +1,105 @@
+"""Differential attention mixer: two softmax maps per head over the same values, one taken off the other.
+
+q = W_q h holds, per query head, two maps of `dim` side by side; k = W_k h likewise per key/value
+head; v = W_v h is one value of `vdim` per key/value head (query head h reads key/value head
+h // (heads / kv_heads)).  Rotary encoding turns the first `rot_dim` dimensions of every map of q
+and k.  With a_m = softmax(q_m . k_m * scale) V over the visible keys (at or before the query,
+within `window` if the layer has one):
+
+    o = a_1 - lambda a_2,   lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff     (one number per layer)
+    out = o / sqrt(mean(o^2) + norm_eps) * (1 - diff)                           (per head, no weight)
+
+then W_o on the concatenated heads.  One stacked matrix serves q|k|v; the cache keeps per token
+and key/value head the two rotated key maps followed by the value
+(`cache.needs.PagedKeysValues`).  lambda is formed once at load, in double.  Scores, softmax, the
+difference and the norm are float.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.needs import PagedKeysValues
+from ..native import ops
+from .base import Part
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+@register_part("mixer", "differential_attention")
+class DifferentialAttention(Part):
+    """params: hidden_size, heads, kv_heads, dim (per map), vdim, scale, diff, window (None | int), norm_eps,
+    position (PartSpec | None).  tensors: q [heads * 2 dim, hidden], k [kv_heads * 2 dim, hidden],
+    v [kv_heads * vdim, hidden], o [hidden, heads * vdim], lq1, lk1, lq2, lk2 [dim]."""
+    category = "mixer"
+    native_libraries = ("diff_attention",)
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.kv_heads = int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.scale, self.diff = float(p["scale"]), float(p["diff"])
+        self.window = p.get("window")
+        self.norm_eps = float(p["norm_eps"])
+        if self.heads % self.kv_heads:
+            raise ValueError(f"differential_attention: {self.heads} heads are not a multiple of "
+                             f"{self.kv_heads} kv heads")
+        if self.vdim > 256 or self.dim > 4096:
+            raise ValueError(f"differential_attention: vdim {self.vdim} / dim {self.dim} are beyond the kernels' "
+                             f"limits of 256 / 4096")
+        self.position = build_part("position", p["position"], ctx) if p.get("position") else None
+        if self.position is not None and self.position.rot_dim > self.dim:
+            raise ValueError("differential_attention: the position encoding turns more dimensions than a map has")
+        self.q_cols = self.heads * 2 * self.dim
+        self.cols = self.q_cols + self.kv_heads * (2 * self.dim + self.vdim)
+        self.qkv = self.o = None
+        self.lam = None
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def cache_need(self):
+        return PagedKeysValues(self.kv_heads, 2 * self.dim, self.vdim, self.window)
+
+    def weight_shapes(self):
+        w = self.hidden
+        shapes = {"q": (self.q_cols, w), "k": (self.kv_heads * 2 * self.dim, w), "v": (self.kv_heads * self.vdim, w),
+                  "o": (w, self.heads * self.vdim)}
+        shapes.update({s: (self.dim,) for s in ("lq1", "lk1", "lq2", "lk2")})
+        return shapes
+
+    def load(self, tensors):
+        mats = [tensors["q"], tensors["k"], tensors["v"]]
+        if len({m.dtype for m in mats}) != 1:
+            raise ValueError("differential_attention: q, k and v matrices must be stored in one dtype")
+        self.qkv = Linear(mats)
+        self.o = Linear([tensors["o"]])
+        lq1, lk1, lq2, lk2 = (tensors[s].double().cpu() for s in ("lq1", "lk1", "lq2", "lk2"))
+        self.lam = math.exp(float((lq1 * lk1).sum())) - math.exp(float((lq2 * lk2).sum())) + self.diff
+
+    def reserve(self, limits):
+        for lin in (self.qkv, self.o):
+            if lin is not None:
+                lin.reserve(self.ctx.dtype, limits.max_tokens)
+
+    def forward(self, h, out, step, cache):
+        n = h.shape[0]
+        dt = self.ctx.dtype
+        ws = step.workspace
+        qkv = ws.rows("diff_qkv", n, self.cols, dt)
+        self.qkv.forward(h, qkv)
+        if self.position is not None:
+            cos, sin = self.position.tables()
+            rot = self.position.rot_dim
+        else:
+            cos, sin, rot = step.no_rotation, step.no_rotation, 0
+        ops.diff_prep(qkv, self.heads, self.kv_heads, self.dim, self.vdim, rot, cos, sin, step.positions,
+                      cache.slots, cache.tensor, cache.page_size)
+        ctx = ws.rows("diff_ctx", n, self.heads * self.vdim, dt)
+        ops.diff_attention_simt(qkv, ctx, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
+                                self.kv_heads, self.dim, self.vdim, self.window, self.scale, self.lam, self.norm_eps,
+                                1.0 - self.diff, cache.page_size)
+        return self.o.forward(ctx, out, defer=True)

@@ -1,6 +1,6 @@
 """Embedding and output head.
 
-Embedding: x = table[ids], no scaling (fastllm_py/model.py:447).  Head:
+Embedding: x = table[ids] (fastllm_py/model.py:447), times `scale` for designs that scale it.  Head:
 logits = x @ W^T in float, no bias (model.py:476), then, for a head with a
 `softcap` c, logits <- c * tanh(logits / c); with tied
 embeddings the head's matrix is the embedding table itself (model.py:228-231),
@@ -15,7 +15,7 @@ from .registry import register_part
 
 @register_part("embedding", "table")
 class Embedding(Part):
-    """params: vocab_size, hidden_size.  tensors: weight [vocab, hidden]."""
+    """params: vocab_size, hidden_size, scale (1: none).  tensors: weight [vocab, hidden]."""
     category = "embedding"
     takes_fed_tokens = True              # an id -1 - r is taken from row r of step.token_feed
 
@@ -23,6 +23,7 @@ class Embedding(Part):
         super().__init__(spec, ctx)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.scale = float(spec.params.get("scale", 1.0))
         self.table = None
 
     def weight_shapes(self):
@@ -32,7 +33,7 @@ class Embedding(Part):
         self.table = tensors["weight"]
 
     def forward(self, step, out):
-        ops.embed(self.table, step.token_ids, out, step.status, getattr(step, "token_feed", None))
+        ops.embed(self.table, step.token_ids, out, step.status, getattr(step, "token_feed", None), self.scale)
 
 
 @register_part("head", "linear")

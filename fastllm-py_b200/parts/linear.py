@@ -97,10 +97,10 @@ class Linear:
                                  cos, sin, positions, slots, cache, page_size)
         return False
 
-    def forward_gated(self, a: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> bool:
-        """For a Linear that stacks a gate and an up matrix: out = act(a gate^T) * (a up^T)
-        in one tensor-core kernel.  False (nothing done) when that kernel does not apply; the
+    def forward_gated(self, a: torch.Tensor, out: torch.Tensor, activation: str = "silu", params=(0.0, 0.0)) -> bool:
+        """For a Linear that stacks a gate and an up matrix: out = f(a gate^T, a up^T) (f = act(g) * u, or the
+        clamped swish unit with its `params`) in one tensor-core kernel.  False (nothing done) when that kernel does not apply; the
         caller then takes `forward` and the activation kernel."""
         if a.dtype == torch.bfloat16 and self.dtype == torch.bfloat16:
-            return _gemm_tc().gemm_swiglu(a, self._tensor_core().weight, out, activation)
+            return _gemm_tc().gemm_swiglu(a, self._tensor_core().weight, out, activation, params)
         return False

@@ -1,9 +1,10 @@
-"""Gated feed-forward: down( act(gate(h)) * up(h) ), no biases; SwiGLU when act is silu.
+"""Gated feed-forward: down( f(gate(h), up(h)) ), no biases; f = act(g) * u, SwiGLU when act is silu,
+or the clamped swish unit (`native.ops.ACTIVATIONS`), whose two constants are `activation_params`.
 
 fastllm_py/model.py:432-435 with the activation of
 fastllm_py/kernels/ops.py:157-163: g / (1 + exp(-g)) * u in float.  gate and up
 are stacked into one matrix so that one product serves both, with the activation
-(`activation`: "silu", "relu", "gelu_tanh") in the product's epilogue where the
+(`activation`: "silu", "relu", "gelu_tanh", "clamped_swish") in the product's epilogue where the
 tensor-core kernel takes the problem, else product and one activation kernel."""
 from __future__ import annotations
 
@@ -16,7 +17,7 @@ from .registry import register_part
 @register_part("feed_forward", "glu")
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
-    """params: hidden_size, intermediate_size, activation ("silu").  tensors: gate, up [I, hidden], down [hidden, I]."""
+    """params: hidden_size, intermediate_size, activation ("silu"), activation_params ((0, 0)).  tensors: gate, up [I, hidden], down [hidden, I]."""
     category = "feed_forward"
 
     def __init__(self, spec, ctx):
@@ -25,6 +26,7 @@ class SwiGLU(Part):
         self.inter = int(spec.params["intermediate_size"])
         self.activation = spec.params.get("activation", "silu")
         ops.activation_code(self.activation)
+        self.activation_params = tuple(float(v) for v in spec.params.get("activation_params", (0.0, 0.0)))
         self.gate_up = None
         self.down = None
 
@@ -48,12 +50,12 @@ class SwiGLU(Part):
         dt = self.ctx.dtype
         act = step.workspace.rows("ffn_act", n, self.inter, dt)
         silu = self.activation == "silu"
-        if self.gate_up.forward_gated(h, act, self.activation):      # product and activation in one kernel
+        if self.gate_up.forward_gated(h, act, self.activation, self.activation_params):   # product and activation in one kernel
             return self.down.forward(act, out, defer=True)
         gu = step.workspace.rows("gate_up", n, 2 * self.inter, dt)
         partial = self.gate_up.forward(h, gu, defer=silu)
         if not silu:
-            ops.glu(gu, act, self.activation)
+            ops.glu(gu, act, self.activation, self.activation_params)
         elif partial is None:
             ops.swiglu(gu, act)
         else:

@@ -4,9 +4,12 @@ gated feed-forwards and adds their outputs up with the router's weights.
 Router: logits z = W_r h in float; scores s = sigmoid(z) (`score`: "sigmoid" or
 "softmax" over the experts); the `top` experts with the largest s + bias are
 chosen, where the bias (`correction`, a stored vector) steers the choice only;
-the weights are the chosen experts' s, renormalised to sum 1 only if
-`renormalise` says so.  Expert e: W_down,e (act(W_gate,e h) * (W_up,e h)), no
-biases.  The experts' matrices are stacked at load into [experts, 2 ff, hidden]
+the weights are the chosen experts' s, divided by their sum (+ `renormalise_eps`)
+only if `renormalise` says so.  With `groups`, the experts form that many equal
+groups of neighbours, a group's score is the largest s + bias in it, and only
+experts of the `keep_groups` best groups can be chosen.  Expert e:
+W_down,e f(W_gate,e h, W_up,e h) with f = act(g) * u or the clamped swish unit
+(`native.ops.ACTIVATIONS`), no biases.  The experts' matrices are stacked at load into [experts, 2 ff, hidden]
 (gate rows, then up rows) and [experts, hidden, ff].
 
 Two ways through the experts.  Few tokens (decode steps): one launch over
@@ -28,7 +31,8 @@ from .registry import register_part
 
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(Part):
-    """params: hidden_size, experts, top, expert_ff, activation ("silu"), score ("sigmoid"), renormalise (False),
+    """params: hidden_size, experts, top, expert_ff, activation ("silu"), activation_params ((0, 0)), score ("sigmoid"),
+    renormalise (False), renormalise_eps (0), groups (None), keep_groups (None: all),
     choice_bias (True: a `correction` tensor is added to the scores for the choice).
     tensors: router [experts, hidden], correction [experts] (if choice_bias), and per expert i
     gate.i, up.i [ff, hidden], down.i [hidden, ff]."""
@@ -44,6 +48,10 @@ class RoutedExperts(Part):
         self.ff = int(p["expert_ff"])
         self.activation = p.get("activation", "silu")
         ops.activation_code(self.activation)
+        self.activation_params = tuple(float(v) for v in p.get("activation_params", (0.0, 0.0)))
+        self.groups = p.get("groups")
+        self.keep_groups = p.get("keep_groups") or self.groups
+        self.renormalise_eps = float(p.get("renormalise_eps", 0.0))
         self.score = p.get("score", "sigmoid")
         if self.score not in ("sigmoid", "softmax"):
             raise ValueError(f"routed_experts: score {self.score!r} is not 'sigmoid' or 'softmax'")
@@ -51,6 +59,10 @@ class RoutedExperts(Part):
         self.choice_bias = bool(p.get("choice_bias", True))
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"routed_experts: top {self.top} of {self.experts} experts")
+        if self.groups is not None and (self.experts % self.groups or not 1 <= self.keep_groups <= self.groups or
+                                        self.keep_groups * (self.experts // self.groups) < self.top):
+            raise ValueError(f"routed_experts: {self.keep_groups} of {self.groups} groups over {self.experts} experts "
+                             f"cannot give {self.top} choices")
         if self.hidden * 4 > 48 * 1024:
             raise ValueError(f"routed_experts: hidden size {self.hidden} exceeds the kernels' 12288")
 
@@ -103,11 +115,13 @@ class RoutedExperts(Part):
         weights = ws.rows("moe_weights", n, padded, torch.float32).view(-1)[:n * self.top].view(n, self.top)
         logits = ws.rows("moe_logits", n, self.experts, torch.float32)
         self.router.forward(h, logits)                       # float accumulation, float logits
-        ops.moe_pick(logits, self.correction, chosen, weights, self.top, self.score == "softmax", self.renormalise)
+        ops.moe_pick(logits, self.correction, chosen, weights, self.top, self.score == "softmax", self.renormalise,
+                     self.groups, self.keep_groups, self.renormalise_eps)
         if n * self.top >= self.GROUP_FROM and self._grouped(h.dtype):
             ints, act, y = self._group_buffers(n, h.device)
-            ops.moe_experts_grouped(h, self.gate_up, self.down, chosen, weights, ints, act, y, out, self.activation)
+            ops.moe_experts_grouped(h, self.gate_up, self.down, chosen, weights, ints, act, y, out, self.activation,
+                                    self.activation_params)
             return None
         act = ws.rows("moe_act", n, self.top * self.ff, torch.float32)
-        ops.moe_experts(h, self.gate_up, self.down, chosen, weights, act, out, self.activation)
+        ops.moe_experts(h, self.gate_up, self.down, chosen, weights, act, out, self.activation, self.activation_params)
         return None

@@ -16,6 +16,7 @@ class RMSNorm(Part):
     category = "norm"
     takes_partial = True                 # split-K partial sums are added while the row is read
     takes_post_norm = True               # a pending sum that passes another RMSNorm first: one kernel does both
+    takes_extra = True                   # two tensors pending: both are added while the row is read
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -34,6 +35,12 @@ class RMSNorm(Part):
         With `rows` (int32 indices) only those rows are normed, into out[0..m), and the
         pending sum (a tensor then: `ResidualStream.norm_into` sees to it) stays pending."""
         post = getattr(stream, "pending_norm", None)
+        if getattr(stream, "extra", None) is not None:
+            # two sums pending (tensors; `ResidualStream.norm_into` sees to it): x += pending + extra; out = self(x)
+            ops.norm_pair(stream.x, stream.pending, stream.extra, self.weight, None, out, None, self.eps, rows)
+            if rows is None:
+                stream.pending = stream.extra = None
+            return
         if stream.pending is not None and post is not None:
             # x += post(pending); out = self(x): the layer norms the sublayer's output before adding it
             if not isinstance(stream.pending, torch.Tensor):         # split-K partial sums (never with rows)
@@ -60,3 +67,14 @@ class RMSNorm(Part):
         """stream.x += rmsnorm(stream.pending) * weight: this part as the norm of a sublayer's output."""
         ops.sandwich_norm(stream.x, stream.pending, self.weight, self.eps, None, 0.0, None)
         stream.pending = stream.pending_norm = None
+
+    def pairs_with(self, other) -> bool:
+        """Whether `apply_pair` can norm a row for this part and `other` at once."""
+        return isinstance(other, RMSNorm) and other.size == self.size and other.eps == self.eps and \
+            other.weight.dtype == self.weight.dtype
+
+    def apply_pair(self, stream, other, out, out_other):
+        """x += pending (+ extra); out = self(x), out_other = other(x): the two norms share the row's root
+        mean square, so one pass serves both.  The pending sum must be a tensor (or none) without a norm of its own."""
+        ops.norm_pair(stream.x, stream.pending, stream.extra, self.weight, other.weight, out, out_other, self.eps)
+        stream.pending = stream.extra = None
