@@ -8,16 +8,18 @@ PART_LIBRARIES = ["rope_kv", "attention_simt", "delta_rule", "latent_attention",
 DEFAULT_HEAD_DIMS = (128,)
 
 
-def all_libraries(head_dims=DEFAULT_HEAD_DIMS, latent_sizes=((512, 64),)) -> list:
-    """Every source; the attention kernels for `head_dims` and the tensor-core latent attention for
-    `latent_sizes` ((latent size, rotated key size) pairs), which are compiled per size."""
+def all_libraries(head_dims=DEFAULT_HEAD_DIMS, latent_sizes=((512, 64),), diff_sizes=((64, 128),)) -> list:
+    """Every source; the attention kernels for `head_dims`, the tensor-core latent attention for
+    `latent_sizes` ((latent size, rotated key size) pairs) and the tensor-core differential attention for
+    `diff_sizes` ((map size, value size) pairs), which are compiled per size."""
     from .attention import libraries as attention_libraries
-    from .ops import latent_tc_library
+    from .ops import diff_tc_library, latent_tc_library
 
     libs = [(name, {}) for name in BASE_LIBRARIES + PART_LIBRARIES + BF16_LIBRARIES]
     for d in head_dims:
         libs += attention_libraries(d)
     libs += [latent_tc_library(rank, rot) for rank, rot in latent_sizes]
+    libs += [diff_tc_library(dim, vdim) for dim, vdim in diff_sizes]
     return libs
 
 

@@ -337,6 +337,32 @@ def diff_attention_simt(q, out, cache, block_table, tok_req, positions, heads, k
            "diff_attention_simt")
 
 
+def diff_tc_takes(dtype, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core differential attention serves this number format and these sizes."""
+    return dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 128 and 16 <= vdim <= 128
+
+
+def diff_tc_library(dim: int, vdim: int):
+    return "diff_attention_tc", {"DIFF_DIM": dim, "DIFF_VDIM": vdim}
+
+
+def diff_attention_tc(q, out, cache, block_table, step, heads, kv_heads, dim, vdim, window, scale, lam, eps, out_scale,
+                      page_size):
+    """`diff_attention_simt` on the tensor cores for bfloat16: 64 rows of a request and one head per block, both
+    maps against the same staged cache rows; one build per (dim, vdim).  Prompt portions and single tokens alike."""
+    _require_cuda(q, out, cache, block_table)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("diff_attention_tc: q, cache and out must be bfloat16")
+    name, defines = diff_tc_library(dim, vdim)
+    fn = _fn(name, "fl_diff_attention_tc", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int,
+                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                            c_float, c_float, c_float, c_void_p], defines)
+    _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size, _ptr(block_table),
+              block_table.stride(0), _ptr(step.req_start), _ptr(step.req_ctx), _ptr(step.req_qlen), step.n_requests,
+              q.shape[0], heads, kv_heads, int(window or 0), float(scale), float(lam), float(eps), float(out_scale),
+              _stream()), "diff_attention_tc")
+
+
 # ------------------------------------------------------------------ retention
 
 def retention_prep(proj, work, heads, dim, rot, cos, sin, positions, k_scale):

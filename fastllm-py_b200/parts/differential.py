@@ -13,6 +13,10 @@ then W_o on the concatenated heads.  One stacked matrix serves q|k|v; the cache 
 and key/value head the two rotated key maps followed by the value
 (`cache.needs.PagedKeysValues`).  lambda is formed once at load, in double.  Scores, softmax, the
 difference and the norm are float.
+
+In bfloat16, with map and value sizes that are multiples of 16 up to 128, attention runs on the
+tensor cores (`csrc/diff_attention_tc.cu`, one build per pair of sizes); everything else, and the
+32-bit path, takes the CUDA-core kernel.
 """
 from __future__ import annotations
 
@@ -80,10 +84,16 @@ class DifferentialAttention(Part):
         lq1, lk1, lq2, lk2 = (tensors[s].double().cpu() for s in ("lq1", "lk1", "lq2", "lk2"))
         self.lam = math.exp(float((lq1 * lk1).sum())) - math.exp(float((lq2 * lk2).sum())) + self.diff
 
+    def _tc(self) -> bool:
+        return ops.diff_tc_takes(self.ctx.dtype, self.dim, self.vdim)
+
     def reserve(self, limits):
         for lin in (self.qkv, self.o):
             if lin is not None:
                 lin.reserve(self.ctx.dtype, limits.max_tokens)
+        if self.ctx.device.type == "cuda" and self._tc():
+            from ..native.build import load_library
+            load_library(*ops.diff_tc_library(self.dim, self.vdim))        # built now, not inside the first step
 
     def forward(self, h, out, step, cache):
         n = h.shape[0]
@@ -99,6 +109,11 @@ class DifferentialAttention(Part):
         ops.diff_prep(qkv, self.heads, self.kv_heads, self.dim, self.vdim, rot, cos, sin, step.positions,
                       cache.slots, cache.tensor, cache.page_size)
         ctx = ws.rows("diff_ctx", n, self.heads * self.vdim, dt)
+        if self._tc():
+            ops.diff_attention_tc(qkv, ctx, cache.tensor, cache.block_table, step, self.heads, self.kv_heads, self.dim,
+                                  self.vdim, self.window, self.scale, self.lam, self.norm_eps, 1.0 - self.diff,
+                                  cache.page_size)
+            return self.o.forward(ctx, out, defer=True)
         ops.diff_attention_simt(qkv, ctx, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
                                 self.kv_heads, self.dim, self.vdim, self.window, self.scale, self.lam, self.norm_eps,
                                 1.0 - self.diff, cache.page_size)

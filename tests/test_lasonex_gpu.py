@@ -352,3 +352,53 @@ def test_clamped_unit_and_pair_norm_kernels(dtype):
     ops.norm_pair(xs, d1, d2, w1, None, few, None, 1e-5, rows)
     assert torch.equal(xs, x)                                               # gathered rows leave the stream alone
     assert float((few.double() - (normed * w1.double())[rows.cpu().long()]).abs().max()) <= 4 * tol
+
+
+@pytest.mark.parametrize("dim,vdim,window", [(32, 64, 70), (16, 16, None), (64, 128, 33), (48, 80, 81)])
+def test_tensor_core_attention_equals_the_cuda_core_one(dim, vdim, window):
+    """Scattered pages, a prompt portion behind cached tokens beside single tokens, a standout key just
+    inside the window of one query and just outside that of the next."""
+    from types import SimpleNamespace
+
+    from fastllm_py_b200.native import ops
+
+    gen = torch.Generator().manual_seed(dim + vdim)
+    heads, kv_heads, page = 4, 2, 16
+    ctx_lens, q_lens = [37, 150, 0, 201], [100, 1, 70, 1]
+    row_w = 2 * dim + vdim
+    n_pages = sum(-(-(c + q) // page) for c, q in zip(ctx_lens, q_lens))
+    order = torch.randperm(n_pages + 5, generator=gen)[:n_pages].tolist()
+    cache = (torch.randn(n_pages + 5, kv_heads, page, row_w, generator=gen) * 0.7).to(torch.bfloat16)
+    bt = torch.zeros(4, 16, dtype=torch.int32)
+    for r, (c, ql) in enumerate(zip(ctx_lens, q_lens)):
+        for i in range(-(-(c + ql) // page)):
+            bt[r, i] = order.pop()
+    n = sum(q_lens)
+    q = (torch.randn(n, heads * 2 * dim, generator=gen) * 0.7).to(torch.bfloat16)
+    if window is not None:
+        # request 0, row 60 (position 97): the key at the window's edge answers its first map loudly
+        edge = 97 - window + 1
+        pg, off = int(bt[0, edge // page]), edge % page
+        cache[pg, 0, off, :dim] = q[60, :dim].float().mul(4.0).to(torch.bfloat16)
+    tok_req = torch.tensor(sum(([r] * ql for r, ql in enumerate(q_lens)), []), dtype=torch.int32)
+    positions = torch.tensor(sum((list(range(c, c + ql)) for c, ql in zip(ctx_lens, q_lens)), []), dtype=torch.int32)
+    starts = [0]
+    for ql in q_lens:
+        starts.append(starts[-1] + ql)
+    dev = lambda t: t.cuda()
+    step = SimpleNamespace(req_start=dev(torch.tensor(starts, dtype=torch.int32)),
+                           req_ctx=dev(torch.tensor(ctx_lens, dtype=torch.int32)),
+                           req_qlen=dev(torch.tensor(q_lens, dtype=torch.int32)), n_requests=4)
+    want = torch.empty(n, heads * vdim, dtype=torch.bfloat16, device="cuda")
+    got = torch.empty_like(want)
+    args = (heads, kv_heads, dim, vdim, window, dim ** -0.5, 0.37, 1e-5, 0.6, page)
+    ops.diff_attention_simt(dev(q), want, dev(cache), dev(bt), dev(tok_req), dev(positions), *args)
+    ops.diff_attention_tc(dev(q), got, dev(cache), dev(bt), step, *args)
+    torch.cuda.synchronize()
+    err = (got.float() - want.float()).abs()
+    assert float(err.max()) <= 0.06 and float(err.mean()) <= 0.006, (float(err.max()), float(err.mean()))
+    if window is not None:
+        far = want.clone()
+        ops.diff_attention_simt(dev(q), far, dev(cache), dev(bt), dev(tok_req), dev(positions),
+                                *(args[:4] + (window - 1,) + args[5:]))
+        assert float((far[60].float() - want[60].float()).abs().max()) > 0.3         # the edge key decides row 60
