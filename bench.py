@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--workload decode|serve|67b|tables|hybrid]
+                    [--workload decode|serve|67b|tables|hybrid|lasonex]
 
 The default run is the DeepSeek-LLM-7B sized model (30 layers, hidden 4096,
 32 heads, head size 128, feed-forward 11008, vocabulary 102400) with random
@@ -42,6 +42,8 @@ Two more workloads, each printing one line of its own:
              prompt in portions of 512, decode steps over a grid of batch sizes and context lengths;
   --workload hybrid  the Tigitar hybrid (gated delta rule + latent attention + routed experts) at two widths
                      beside the dense decoder of equal width and depth: prompt and decode steps
+  --workload lasonex the Lasonex design (differential attention + retention in parallel layers, grouped experts)
+                     at the same two widths, beside the Tigitar hybrid and the dense decoder
   --workload 67b     deepseek-llm-67b size (95 layers, hidden 8192, 64 heads over 8 key/value
              heads; 135 GB of weights on the one GPU): a 2048-token prompt step and decode
              steps at batch 1, 8 and 16 with 4000-token contexts, with their roofline fractions.
@@ -654,6 +656,148 @@ def run_hybrid(args, warmup):
     return 0
 
 
+LASONEX_SIZES = {
+    # parallel layers of differential attention and retention at the widths of HYBRID_SIZES; the dense
+    # Llama-style decoder and the Tigitar hybrid of the same width and depth are timed beside them
+    "w2048": dict(width=2048, vocab=32256, layers=8, attention=dict(heads=16, kv_heads=4, dim=64, vdim=128, window=1024),
+                  retention=dict(heads=16, dim=128, vdim=128), dense_ff=5504, experts=32, top=4, expert_ff=1408,
+                  groups=(8, 4)),
+    "w4096": dict(width=4096, vocab=32256, layers=4, attention=dict(heads=32, kv_heads=8, dim=64, vdim=128, window=2048),
+                  retention=dict(heads=32, dim=128, vdim=128), dense_ff=11008, experts=16, top=2, expert_ff=5504,
+                  groups=(4, 2)),
+}
+
+
+def lasonex_config(size):
+    """A Lasonex configuration of `size`: layers cycle through attention + dense, retention + experts,
+    attention + experts, attention + experts (one layer in four is recurrent)."""
+    from fastllm_py_b200.config.lasonex import (ClampedFeedForwardConfig, DifferentialAttentionConfig,
+                                                GroupedExpertsConfig, LasonexConfig, LasonexLayerConfig,
+                                                RetentionConfig, RotationConfig)
+
+    z = LASONEX_SIZES[size]
+    a, r = z["attention"], z["retention"]
+    attention = DifferentialAttentionConfig(a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["dim"] ** -0.5, 0.5,
+                                            a["window"], RotationConfig(50000.0, a["dim"], ("yarn", 8.0, 2048.0, 32.0, 1.0)))
+    decay = tuple(1.0 - 2.0 ** (-5.0 - 6.0 * h / max(1, r["heads"] - 1)) for h in range(r["heads"]))
+    retention = RetentionConfig(r["heads"], r["dim"], r["vdim"], decay, RotationConfig(1e6, r["dim"], None))
+    dense = ClampedFeedForwardConfig(z["dense_ff"], 7.0)
+    routed = GroupedExpertsConfig(z["experts"], z["top"], z["groups"][0], z["groups"][1], z["expert_ff"], 7.0)
+    layers = []
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind == 0:
+            layers.append(LasonexLayerConfig("attention", attention, dense))
+        elif kind == 1:
+            layers.append(LasonexLayerConfig("retention", retention, routed))
+        else:
+            layers.append(LasonexLayerConfig("attention", attention, routed))
+    return LasonexConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, embedding_scale=12.0, layers=tuple(layers))
+
+
+def lasonex_decode_bytes(cfg, batch, context):
+    """Bytes a decode step has to move: the weights it uses once in bfloat16 (of the experts, those that
+    `batch` tokens can reach), every request's retention states read and written in float, and the cache
+    rows (two key maps and a value per key/value head) inside each window."""
+    from fastllm_py_b200.config.lasonex import GroupedExpertsConfig, RetentionConfig
+
+    w, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer.mixer
+        if isinstance(m, RetentionConfig):
+            total += 2 * w * (2 * m.heads * m.dim + 3 * m.heads * m.vdim)
+            total += batch * 2 * 4 * m.heads * m.vdim * m.dim
+        else:
+            total += 2 * w * (m.heads * 2 * m.dim + m.kv_heads * (2 * m.dim + m.vdim) + m.heads * m.vdim)
+            total += batch * min(context, m.window or context) * m.kv_heads * (2 * m.dim + m.vdim) * 2
+        f = layer.mlp
+        if isinstance(f, GroupedExpertsConfig):
+            total += 2 * 3 * w * f.ff * min(f.experts, batch * f.top) + 2 * w * f.experts
+        elif f is not None:
+            total += 2 * 3 * w * f.ff
+    return total + 2 * w * cfg.vocab + 2 * batch * w
+
+
+def lasonex_prefill_flops(cfg, tokens):
+    """Matrix-product FLOPs of a prompt step (projections, feed-forwards, both attention maps over the window,
+    head); the retention recurrence adds 4 dim vdim per head and token."""
+    from fastllm_py_b200.config.lasonex import GroupedExpertsConfig, RetentionConfig
+
+    w, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer.mixer
+        if isinstance(m, RetentionConfig):
+            total += 2 * tokens * w * (2 * m.heads * m.dim + 3 * m.heads * m.vdim) + tokens * m.heads * 4 * m.dim * m.vdim
+        else:
+            total += 2 * tokens * w * (m.heads * 2 * m.dim + m.kv_heads * (2 * m.dim + m.vdim) + m.heads * m.vdim)
+            seen = sum(min(p + 1, m.window or p + 1) for p in range(tokens))
+            total += 2 * m.heads * seen * 2 * (m.dim + m.vdim)
+        f = layer.mlp
+        if isinstance(f, GroupedExpertsConfig):
+            total += 2 * tokens * (3 * w * f.ff * f.top + w * f.experts)
+        elif f is not None:
+            total += 2 * tokens * 3 * w * f.ff
+    return total + 2 * w * cfg.vocab
+
+
+def run_lasonex(args, warmup):
+    """The Lasonex design beside the Tigitar hybrid and the dense decoder of equal width and depth, one JSON
+    line: prompt steps of 512 and 2048 tokens and decode steps at batch 1 and 8 over 2048-token contexts, with
+    each model's fraction of its own roofline (measured tensor peak for prompts, measured copy bandwidth for
+    decode steps)."""
+    from fastllm_py_b200 import LlamaConfig, Model
+
+    pk = peaks()
+    steps = max(8, min(args.steps, 32))
+    out = {}
+    sampler = ClockSampler().start()
+    sampler.__enter__()
+    for size in (args.size.split(",") if args.size else list(LASONEX_SIZES)):
+        z, hz = LASONEX_SIZES[size], HYBRID_SIZES[size]
+        llama = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                            num_layers=z["layers"], hidden_size=z["width"], vocab_size=z["vocab"], rope_theta=10000.0,
+                            rms_norm_eps=1e-6, max_position_embeddings=4096, **hz["llama"])
+        models = [("lasonex", lasonex_config(size), lasonex_prefill_flops, lasonex_decode_bytes),
+                  ("hybrid", hybrid_config(size), hybrid_prefill_flops, hybrid_decode_bytes),
+                  ("dense", llama, prefill_flops, decode_bytes)]
+        res = {}
+        for name, cfg, flops_of, bytes_of in models:
+            if args.only and name not in args.only.split(","):
+                continue
+            model = Model.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=8 * (CONTEXT + 256),
+                                      max_requests=8, max_batched_tokens=2048, max_model_len=4096,
+                                      cuda_graph=not args.no_graph)
+            r = {"prompt_step": {}, "decode": {}}
+            for t in (512, 2048):
+                ms, _ = time_prefill(model, t, 8, 3)
+                r["prompt_step"][str(t)] = {"ms": round(ms, 3), "value": round(t * 1000.0 / ms, 1),
+                                            "frac": round(flops_of(cfg, t) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            for b in (1, 8):
+                v, ms, launches, _ = time_decode(model, b, steps, warmup, CONTEXT)
+                ctx = CONTEXT + warmup + (steps + 1) / 2
+                r["decode"][f"{b}x{CONTEXT}"] = {"ms_per_step": round(ms, 3), "value": round(v, 1),
+                                                 "launches_per_step": launches // steps,
+                                                 "frac": round(bytes_of(cfg, b, ctx) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+            res[name] = r
+            del model
+            import gc
+
+            import torch
+            gc.collect()
+            torch.cuda.empty_cache()
+        out[size] = res
+    sampler.__exit__()
+    print(json.dumps({
+        "metric": "prompt and decode steps of the Lasonex design beside the Tigitar hybrid and the dense decoder "
+                  "of equal size, bf16",
+        "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": steps, "warmup": warmup,
+        "config": {"sizes": {k: dict(LASONEX_SIZES[k]) for k in out}, "page_size": 16,
+                   "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"],
+                   "cuda_graph": not args.no_graph},
+        "sizes": out, "clocks": sampler.summary()}))
+    return 0
+
+
 def reference_cpu_path(ref_root, layers=1, context=256, decode_tokens=8):
     """fastllm-py's own NumPy model code (its CPU device, float32) timed at DeepSeek-LLM-7B layer
     sizes: `layers` of the 30 layers, one sequence (that path has no batch), a `context`-token
@@ -790,10 +934,11 @@ def main():
                     help="run fewer layers of the same sizes (the line names both numbers)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables", "hybrid"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables", "hybrid", "lasonex"],
                     help="decode: the headline line (DeepSeek-LLM-7B size); serve: continuous batching at "
                          "deepseek-coder-1.3b size; 67b: prompt and decode steps at deepseek-llm-67b size")
-    ap.add_argument("--size", default="", help="hybrid: which sizes (w2048,w4096; default both)")
+    ap.add_argument("--size", default="", help="hybrid, lasonex: which sizes (w2048,w4096; default both)")
+    ap.add_argument("--only", default="", help="lasonex: which of the models timed side by side (lasonex,hybrid,dense)")
     ap.add_argument("--requests", type=int, default=128, help="serve: how many requests")
     ap.add_argument("--rate", type=float, default=16.0, help="serve: mean arrivals a second")
     ap.add_argument("--reference-cpu", action="store_true",
@@ -812,6 +957,8 @@ def main():
         return run_67b(args, warmup)
     if args.workload == "tables":
         return run_tables(args, warmup)
+    if args.workload == "lasonex":
+        return run_lasonex(args, warmup)
     if args.workload == "hybrid":
         return run_hybrid(args, warmup)
     args.layers = args.layers or MODEL_7B["num_layers"]

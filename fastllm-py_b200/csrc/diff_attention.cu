@@ -16,6 +16,11 @@
 //                        order depends on the token's own position only (cuts and batches agree bit
 //                        for bit)
 //
+//   diff_decode          single tokens with their keys split over blocks: per (token, key/value head, split of
+//                        128 keys at a multiple of 128 of the absolute position) the maxima, sums and weighted
+//                        values of both maps of every query head of the group, so that a cache row is read once
+//                        for the group; diff_decode_merge adds the splits up and does the difference and the norm
+//
 // Scores, softmax, the difference and the norm are float.
 #include "common.cuh"
 
@@ -189,5 +194,191 @@ FL_API int fl_diff_attention_simt(const void* q, int dtype, long q_ld, void* out
                                            (const T*)q, q_ld, (T*)out, out_ld, (const T*)cache, page_stride, page_size,
                                            block_table, bt_stride, tok_req, positions, heads, kv_heads, dim, vdim,
                                            window, scale, lambda, eps, out_scale));
+    return 0;
+}
+
+// ------------------------------------------------------------------ single tokens, keys split over blocks
+#define DIFF_SPLIT 128           // keys of a split: one per thread
+
+// GROUP: query heads per key/value head, rounded up to a power of two (at most 8); pair hm = 2 * head in group + map.
+// partial: [n_decode][heads][2 maps][n_splits][vdim + 2] floats: maximum, sum, weighted values.
+template <typename T, int GROUP>
+__global__ void __launch_bounds__(DIFF_SPLIT) diff_decode_kernel(
+    const T* __restrict__ q, long q_ld, const T* __restrict__ cache, long page_stride, int page_size,
+    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req, const int* __restrict__ positions,
+    const int* __restrict__ decode_tokens, float* __restrict__ partial, int n_splits, int heads, int kv_heads, int dim,
+    int vdim, int window, float scale) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int GM = 2 * GROUP;
+    extern __shared__ __align__(16) unsigned char dec_smem[];
+    long* off_s = reinterpret_cast<long*>(dec_smem);                  // [SPLIT] element offset of each row's value part
+    float* p_s = reinterpret_cast<float*>(off_s + DIFF_SPLIT);        // [SPLIT][GM] numerators
+    float* red_s = p_s + DIFF_SPLIT * GM;                             // [4 warps][GM]
+    float* q_s = red_s + 4 * GM;                                      // [GM][dim]
+    const int t = decode_tokens[blockIdx.x], g = blockIdx.y, split = blockIdx.z, tid = threadIdx.x;
+    const int group = heads / kv_heads;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = (lo / DIFF_SPLIT + split) * DIFF_SPLIT;
+    const int row_w = 2 * dim + vdim;
+    float* out = partial + ((((long)blockIdx.x * heads + (long)g * group) * 2) * n_splits + split) * (vdim + 2);
+    const long hm_stride = (long)n_splits * (vdim + 2);               // from one (head, map) pair to the next
+    if (first > pos) {                                                // nothing of this token in the split
+        for (int hm = tid; hm < 2 * group; hm += DIFF_SPLIT) {
+            out[hm * hm_stride] = -CUDART_INF_F;
+            out[hm * hm_stride + 1] = 0.0f;
+        }
+        return;
+    }
+    for (int i = tid; i < 2 * group * dim; i += DIFF_SPLIT)
+        q_s[i] = to_f32<T>(q[(long)t * q_ld + (long)g * group * 2 * dim + i]);
+    __syncthreads();
+    const int* bt = block_table + (long)tok_req[t] * bt_stride;
+    const int j = first + tid;
+    const bool valid = j >= lo && j <= pos;
+    float s[GM];
+#pragma unroll
+    for (int hm = 0; hm < GM; ++hm) s[hm] = 0.0f;
+    if (valid) {
+        const long off = (long)bt[j / page_size] * page_stride + ((long)g * page_size + j % page_size) * row_w;
+        off_s[tid] = off + 2 * dim;
+        const T* kp = cache + off;
+        for (int d = 0; d < dim; ++d) {
+            const float k1 = to_f32<T>(kp[d]), k2 = to_f32<T>(kp[dim + d]);
+#pragma unroll
+            for (int hh = 0; hh < GROUP; ++hh)
+                if (hh < group) {
+                    s[2 * hh] += q_s[(2 * hh) * dim + d] * k1;
+                    s[2 * hh + 1] += q_s[(2 * hh + 1) * dim + d] * k2;
+                }
+        }
+    }
+    const int warp = tid >> 5, lane = tid & 31;
+    float m[GM];
+#pragma unroll
+    for (int hm = 0; hm < GM; ++hm) {
+        s[hm] = valid ? s[hm] * scale : -CUDART_INF_F;
+        const float w = warp_max(s[hm]);
+        if (lane == 0) red_s[warp * GM + hm] = w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hm = 0; hm < GM; ++hm) {
+        m[hm] = fmaxf(fmaxf(red_s[hm], red_s[GM + hm]), fmaxf(red_s[2 * GM + hm], red_s[3 * GM + hm]));
+        const float p = valid ? expf(s[hm] - m[hm]) : 0.0f;          // (some key of the split is valid: m is finite)
+        p_s[tid * GM + hm] = p;
+        s[hm] = warp_sum(p);
+    }
+    __syncthreads();                                                  // red_s was read; p_s and off_s are written
+#pragma unroll
+    for (int hm = 0; hm < GM; ++hm)
+        if (lane == 0) red_s[warp * GM + hm] = s[hm];
+    __syncthreads();
+#pragma unroll
+    for (int hm = 0; hm < GM; ++hm)
+        if (tid == hm && hm < 2 * group) {                            // (m is the same in every thread)
+            out[hm * hm_stride] = m[hm];
+            out[hm * hm_stride + 1] = red_s[hm] + red_s[GM + hm] + red_s[2 * GM + hm] + red_s[3 * GM + hm];
+        }
+    const int j_begin = max(0, lo - first), j_end = min(DIFF_SPLIT, pos - first + 1);
+    for (int d = tid; d < vdim; d += DIFF_SPLIT) {
+        float acc[GM];
+#pragma unroll
+        for (int hm = 0; hm < GM; ++hm) acc[hm] = 0.0f;
+        for (int jj = j_begin; jj < j_end; ++jj) {
+            const float v = to_f32<T>(cache[off_s[jj] + d]);
+#pragma unroll
+            for (int hm = 0; hm < GM; ++hm) acc[hm] += p_s[jj * GM + hm] * v;
+        }
+#pragma unroll
+        for (int hm = 0; hm < GM; ++hm)
+            if (hm < 2 * group) out[hm * hm_stride + 2 + d] = acc[hm];
+    }
+}
+
+// One block per (token, query head): both maps' splits added up, the difference, the norm.
+template <typename T>
+__global__ void __launch_bounds__(128) diff_decode_merge_kernel(const float* __restrict__ partial, int n_splits,
+                                                                const int* __restrict__ decode_tokens, T* __restrict__ out,
+                                                                long out_ld, int heads, int vdim, float lambda, float eps,
+                                                                float out_scale) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float scratch[32];
+    const int h = blockIdx.y, tid = threadIdx.x;
+    const float* base = partial + (((long)blockIdx.x * heads + h) * 2) * n_splits * (vdim + 2);
+    float top[2] = {-CUDART_INF_F, -CUDART_INF_F}, sum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int mp = 0; mp < 2; ++mp) {
+        const float* pm = base + (long)mp * n_splits * (vdim + 2);
+        for (int s = 0; s < n_splits; ++s) top[mp] = fmaxf(top[mp], pm[(long)s * (vdim + 2)]);
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = pm[(long)s * (vdim + 2)];
+            if (ms != -CUDART_INF_F) sum[mp] += pm[(long)s * (vdim + 2) + 1] * expf(ms - top[mp]);
+        }
+    }
+    float o[2] = {0.0f, 0.0f}, ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int d = tid + c * 128;
+        if (d >= vdim) continue;
+        float a[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int mp = 0; mp < 2; ++mp) {
+            const float* pm = base + (long)mp * n_splits * (vdim + 2);
+            for (int s = 0; s < n_splits; ++s) {
+                const float ms = pm[(long)s * (vdim + 2)];
+                if (ms != -CUDART_INF_F) a[mp] += pm[(long)s * (vdim + 2) + 2 + d] * expf(ms - top[mp]);
+            }
+        }
+        o[c] = a[0] / sum[0] - lambda * (a[1] / sum[1]);
+        ss += o[c] * o[c];
+    }
+    ss = block_sum(ss, scratch);
+    const float f = out_scale / sqrtf(ss / (float)vdim + eps);
+    T* dst = out + (long)decode_tokens[blockIdx.x] * out_ld + (long)h * vdim;
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+        if (tid + c * 128 < vdim) dst[tid + c * 128] = from_f32<T>(o[c] * f);
+}
+
+// Whether the split-key kernels take a layer of these sizes.
+FL_API int fl_diff_decode_takes(int heads, int kv_heads, int dim, int vdim) {
+    const int group = kv_heads > 0 && heads % kv_heads == 0 ? heads / kv_heads : 0;
+    return group >= 1 && group <= 8 && vdim >= 1 && vdim <= 256 && dim >= 1 &&
+           (size_t)DIFF_SPLIT * (sizeof(long) + 16 * sizeof(float)) + (size_t)(64 + 16 * dim) * sizeof(float) <= 48 * 1024;
+}
+
+// The rows `decode_tokens` (n_decode of them, each the single token of its request) of q get attention over their
+// requests' cache rows; n_splits must reach every token's last key: (longest visible span - 1) / 128 + 2 does.
+// partial: n_decode * heads * 2 * n_splits * (vdim + 2) floats.
+FL_API int fl_diff_decode(const void* q, int dtype, long q_ld, void* out, long out_ld, const void* cache, long page_stride,
+                          int page_size, const int* block_table, int bt_stride, const int* tok_req, const int* positions,
+                          const int* decode_tokens, int n_decode, float* partial, int n_splits, int heads, int kv_heads,
+                          int dim, int vdim, int window, float scale, float lambda, float eps, float out_scale,
+                          cudaStream_t stream) {
+    if (n_decode <= 0) return 0;
+    if (!fl_diff_decode_takes(heads, kv_heads, dim, vdim) || n_splits < 1 || n_splits > 65535 || kv_heads > 65535)
+        return (int)cudaErrorInvalidValue;
+    const int group = heads / kv_heads;
+    const int gp = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
+    const size_t smem = (size_t)DIFF_SPLIT * (sizeof(long) + 2 * gp * sizeof(float)) + (size_t)(8 * gp + 2 * gp * dim) * sizeof(float);
+    dim3 grid(n_decode, kv_heads, n_splits);
+    int rc = 0;
+#define FL_DIFF_DECODE(G)                                                                                            \
+    FL_DISPATCH(dtype, T, rc = fl_launch(diff_decode_kernel<T, G>, grid, dim3(DIFF_SPLIT), smem, stream, (const T*)q, \
+                                         q_ld, (const T*)cache, page_stride, page_size, block_table, bt_stride,      \
+                                         tok_req, positions, decode_tokens, partial, n_splits, heads, kv_heads, dim, \
+                                         vdim, window, scale))
+    if (gp == 1) { FL_DIFF_DECODE(1); }
+    else if (gp == 2) { FL_DIFF_DECODE(2); }
+    else if (gp == 4) { FL_DIFF_DECODE(4); }
+    else { FL_DIFF_DECODE(8); }
+#undef FL_DIFF_DECODE
+    if (rc) return rc;
+    FL_DISPATCH(dtype, T, return fl_launch(diff_decode_merge_kernel<T>, dim3(n_decode, heads), dim3(128), 0, stream,
+                                           (const float*)partial, n_splits, decode_tokens, (T*)out, out_ld, heads, vdim,
+                                           lambda, eps, out_scale));
     return 0;
 }

@@ -9,7 +9,8 @@
 // request's keys in blocks of 64, from the first key any of its rows may see to the last, through the
 // block table: rows cached by earlier steps and the rows this step wrote are read alike, so a portion
 // of a prompt is the same as a whole prompt, and a single decoded token is a tile of one row (warps
-// without rows only help to load).  Key blocks start at multiples of 64 of the absolute position, so
+// without rows only help to load; steps of single tokens have a kernel of their own that splits the keys,
+// diff_attention.cu, and the launcher can leave such requests out).  Key blocks start at multiples of 64 of the absolute position, so
 // the partial maxima and sums a row goes through depend on the row's position only.  A block's rows
 // (both key maps and the value: one piece of memory per token) come by cp.async into a two-stage ring
 // while the block before is multiplied; both maps are multiplied against the same staged values, each
@@ -69,7 +70,8 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
     const bf16* __restrict__ q, long q_ld, bf16* __restrict__ out, long out_ld, const bf16* __restrict__ cache,
     long page_stride, int page_size, int page_shift, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ req_start, const int* __restrict__ req_ctx, const int* __restrict__ req_qlen,
-    int n_requests, int heads, int kv_heads, int window, float scale_log2e, float lambda, float eps, float out_scale) {
+    int n_requests, int include_single, int heads, int kv_heads, int window, float scale_log2e, float lambda, float eps,
+    float out_scale) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ __align__(16) unsigned char dtc_raw[];
@@ -81,7 +83,8 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
     {
         int acc = 0;
         for (int r = 0; r < n_requests; ++r) {
-            const int nt = (req_qlen[r] + DTC_BM - 1) / DTC_BM;
+            const int ql = req_qlen[r];
+            const int nt = (ql > 1 || include_single) ? (ql + DTC_BM - 1) / DTC_BM : 0;
             if ((int)blockIdx.x < acc + nt) { req = r; tile = nt - 1 - ((int)blockIdx.x - acc); break; }
             acc += nt;
         }
@@ -279,12 +282,12 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
 FL_API int fl_diff_attention_tc_dim() { return DIFF_DIM; }
 FL_API int fl_diff_attention_tc_vdim() { return DIFF_VDIM; }
 
-// Every request r of the step gets attention for its rows req_start[r] .. req_start[r] + req_qlen[r] - 1 at
+// Every request r of the step with req_qlen[r] > 1 (or >= 1 with include_single) gets attention for its rows req_start[r] .. req_start[r] + req_qlen[r] - 1 at
 // positions req_ctx[r] + i over its cached rows.  n_tokens bounds the number of 64-row tiles.
 FL_API int fl_diff_attention_tc(const void* q, long q_ld, void* out, long out_ld, const void* cache, long page_stride,
                                 int page_size, const int* block_table, int bt_stride, const int* req_start,
-                                const int* req_ctx, const int* req_qlen, int n_requests, int n_tokens, int heads,
-                                int kv_heads, int window, float scale, float lambda, float eps, float out_scale,
+                                const int* req_ctx, const int* req_qlen, int n_requests, int n_tokens,
+                                int include_single, int heads, int kv_heads, int window, float scale, float lambda, float eps, float out_scale,
                                 cudaStream_t stream) {
     if (n_requests <= 0 || n_tokens <= 0) return 0;
     if (heads > 65535 || heads % kv_heads) return (int)cudaErrorInvalidValue;
@@ -306,6 +309,6 @@ FL_API int fl_diff_attention_tc(const void* q, long q_ld, void* out, long out_ld
     dim3 grid(max_tiles, heads);
     return fl_launch(diff_attention_tc_kernel, grid, dim3(DTC_THREADS), smem, stream, (const bf16*)q, q_ld, (bf16*)out,
                      out_ld, (const bf16*)cache, page_stride, page_size, page_shift, block_table, bt_stride, req_start,
-                     req_ctx, req_qlen, n_requests, heads, kv_heads, window, scale * 1.4426950408889634f, lambda, eps,
-                     out_scale);
+                     req_ctx, req_qlen, n_requests, include_single, heads, kv_heads, window, scale * 1.4426950408889634f,
+                     lambda, eps, out_scale);
 }

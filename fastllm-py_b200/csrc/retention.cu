@@ -6,10 +6,10 @@
 // `k_scale` after the rotation.  The head's o is divided by its root mean square and multiplied by
 // silu(gate).
 //
-//   retention_prep        per (token, q or k head): rotation and scale into a float work row q | k
-//   retention_scan        per (request, head, 32 value columns): the recurrence over the portion's tokens,
+//   retention_prep        per (token, q, k or v head): rotation and scale into a float work row q | k | v
+//   retention_scan        per (request, head, 32 or 16 value columns): the recurrence over the portion's tokens,
 //                         one value column's state spread over eight lanes' registers, the tokens' q, k and
-//                         v staged through shared memory a chunk at a time
+//                         v staged through shared memory a chunk of 16 ahead (cp.async, two buffers)
 //   retention_gated_norm  per (token, head): o / sqrt(mean(o^2) + eps) * silu(gate)
 //
 // A request's state row is [heads][vdim][dim] floats (a column of S is contiguous).  A portion that
@@ -24,12 +24,18 @@
 
 template <typename T>
 __global__ void __launch_bounds__(128) retention_prep_kernel(
-    const T* __restrict__ proj, long ld, float* __restrict__ work, long work_ld, int heads, int dim, int rot,
+    const T* __restrict__ proj, long ld, float* __restrict__ work, long work_ld, int heads, int dim, int vdim, int rot,
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, const int* __restrict__ positions,
     float k_scale) {
     pdl_wait();
     pdl_trigger();
-    const int t = blockIdx.x, unit = blockIdx.y;           // units: q heads, then k heads, in the projection's order
+    const int t = blockIdx.x, unit = blockIdx.y;           // units: q heads, k heads, v heads, in the projection's order
+    if (unit >= 2 * heads) {                               // a value head: widened to float as it is
+        const long off = (long)2 * heads * dim + (long)(unit - 2 * heads) * vdim;
+        for (int j = threadIdx.x; j < vdim; j += blockDim.x)
+            work[(long)t * work_ld + off + j] = to_f32<T>(proj[(long)t * ld + off + j]);
+        return;
+    }
     const int half = rot >> 1;
     const long pos = positions[t];
     const float* cs = cos_table + pos * half;
@@ -45,31 +51,37 @@ __global__ void __launch_bounds__(128) retention_prep_kernel(
     for (int j = rot + threadIdx.x; j < dim; j += blockDim.x) y[j] = to_f32<T>(x[j]) * f;
 }
 
-// proj columns: q (heads x dim) | k (heads x dim) | ...; work columns: q | k (float).
+// proj columns: q (heads x dim) | k (heads x dim) | v (heads x vdim) | ...; work columns: q | k | v (float).
 FL_API int fl_retention_prep(const void* proj, int dtype, long ld, float* work, long work_ld, int n_tokens, int heads,
-                             int dim, int rot, const float* cos_table, const float* sin_table, const int* positions,
-                             float k_scale, cudaStream_t stream) {
+                             int dim, int vdim, int rot, const float* cos_table, const float* sin_table,
+                             const int* positions, float k_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (rot < 0 || rot > dim || (rot & 1) || 2 * heads > 65535) return (int)cudaErrorInvalidValue;
-    FL_DISPATCH(dtype, T, return fl_launch(retention_prep_kernel<T>, dim3(n_tokens, 2 * heads), dim3(128), 0, stream,
-                                           (const T*)proj, ld, work, work_ld, heads, dim, rot, cos_table, sin_table,
-                                           positions, k_scale));
+    if (rot < 0 || rot > dim || (rot & 1) || 3 * heads > 65535) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(dtype, T, return fl_launch(retention_prep_kernel<T>, dim3(n_tokens, 3 * heads), dim3(128), 0, stream,
+                                           (const T*)proj, ld, work, work_ld, heads, dim, vdim, rot, cos_table,
+                                           sin_table, positions, k_scale));
     return 0;
 }
 
-// NI: state elements per lane (dim <= 8 NI).  A lane holds rows part, part + 8, ... of its column.
-template <typename T, int NI>
-__global__ void __launch_bounds__(RET_COLS * RET_PARTS) retention_scan_kernel(
-    const float* __restrict__ qk, long qk_ld, const T* __restrict__ v, long v_ld, float* __restrict__ o, long o_ld,
-    float* __restrict__ state, long state_stride, const float* __restrict__ decay, const int* __restrict__ req_start,
+__device__ __forceinline__ void ret_cp(float* dst, const float* src, int bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+// NI: state elements per lane (dim <= 8 NI); COLS: value columns of a block.  A lane holds rows part, part + 8, ...
+// of its column.  A staged token is dim floats of q, dim of k and COLS of v.
+template <int NI, int COLS>
+__global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
+    const float* __restrict__ qkv, long ld, float* __restrict__ o, long o_ld, float* __restrict__ state,
+    long state_stride, const float* __restrict__ decay, const int* __restrict__ req_start,
     const int* __restrict__ req_ctx, const int* __restrict__ req_qlen, const int* __restrict__ req_slot, int heads,
-    int dim, int vdim) {
+    int dim, int vdim, int vec) {
     pdl_wait();
     pdl_trigger();
-    extern __shared__ float ret_smem[];                    // [CHUNK][2 dim] q | k, then [CHUNK][COLS] v
-    float* qk_s = ret_smem;
-    float* v_s = ret_smem + RET_CHUNK * 2 * dim;
-    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * RET_COLS;
+    extern __shared__ __align__(16) float ret_smem[];      // two buffers of [CHUNK][2 dim + COLS]
+    const int row_w = 2 * dim + COLS;
+    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
     const int tid = threadIdx.x, part = tid & (RET_PARTS - 1), col = col0 + (tid >> 3);
     const int start = req_start[r], qlen = req_qlen[r];
     const bool live = col < vdim;
@@ -82,23 +94,56 @@ __global__ void __launch_bounds__(RET_COLS * RET_PARTS) retention_scan_kernel(
         S[i] = (!fresh && live && d < dim) ? srow[d] : 0.0f;
     }
     const float g = decay[h];
-    for (int base = 0; base < qlen; base += RET_CHUNK) {
+    const long q_off = (long)h * dim, k_off = (long)heads * dim + (long)h * dim;
+    const long v_off = (long)2 * heads * dim + (long)h * vdim + col0;
+    const int v_cols = min(COLS, vdim - col0);
+
+    // stage chunk `base` into buffer `buf`: pieces of 4 floats where every start is 16-byte aligned, else float by float
+    auto stage = [&](int base, int buf) {
+        float* dst = ret_smem + (long)buf * RET_CHUNK * row_w;
         const int n = min(RET_CHUNK, qlen - base);
-        __syncthreads();                                   // the chunk before is read out
-        for (int i = tid; i < n * 2 * dim; i += blockDim.x) {
-            const int c = i / (2 * dim), e = i - c * 2 * dim;
-            const int which = e / dim, d = e - which * dim;
-            qk_s[i] = qk[(long)(start + base + c) * qk_ld + (long)which * heads * dim + (long)h * dim + d];
+        if (vec) {
+            const int per = row_w / 4, qk4 = dim / 4;
+            for (int i = tid; i < n * per; i += blockDim.x) {
+                const int c = i / per, e = i - c * per;
+                const float* src = qkv + (long)(start + base + c) * ld;
+                if (e < qk4) src += q_off + e * 4;
+                else if (e < 2 * qk4) src += k_off + (e - qk4) * 4;
+                else if ((e - 2 * qk4) * 4 < v_cols) src += v_off + (e - 2 * qk4) * 4;
+                else continue;
+                ret_cp(dst + c * row_w + e * 4, src, 16);
+            }
+        } else {
+            for (int i = tid; i < n * row_w; i += blockDim.x) {
+                const int c = i / row_w, e = i - c * row_w;
+                const float* src = qkv + (long)(start + base + c) * ld;
+                if (e < dim) src += q_off + e;
+                else if (e < 2 * dim) src += k_off + (e - dim);
+                else if (e - 2 * dim < v_cols) src += v_off + (e - 2 * dim);
+                else continue;
+                ret_cp(dst + c * row_w + e, src, 4);
+            }
         }
-        for (int i = tid; i < n * RET_COLS; i += blockDim.x) {
-            const int c = i / RET_COLS, j = i - c * RET_COLS;
-            v_s[i] = col0 + j < vdim ? to_f32<T>(v[(long)(start + base + c) * v_ld + (long)h * vdim + col0 + j]) : 0.0f;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    stage(0, 0);
+    int buf = 0;
+    for (int base = 0; base < qlen; base += RET_CHUNK, buf ^= 1) {
+        const int n = min(RET_CHUNK, qlen - base);
+        if (base + RET_CHUNK < qlen) {
+            stage(base + RET_CHUNK, buf ^ 1);              // (its buffer was read out before the last barrier)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        const float* rows = ret_smem + (long)buf * RET_CHUNK * row_w;
+#pragma unroll 4
         for (int c = 0; c < n; ++c) {
-            const float* qs = qk_s + c * 2 * dim;
+            const float* qs = rows + c * row_w;
             const float* ks = qs + dim;
-            const float vj = v_s[c * RET_COLS + (tid >> 3)];
+            const float vj = live ? qs[2 * dim + (tid >> 3)] : 0.0f;
             float acc = 0.0f;
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
@@ -113,6 +158,7 @@ __global__ void __launch_bounds__(RET_COLS * RET_PARTS) retention_scan_kernel(
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             if (part == 0 && live) o[(long)(start + base + c) * o_ld + (long)h * vdim + col] = acc;
         }
+        __syncthreads();                                   // the buffer is staged into again next round
     }
     if (live) {
 #pragma unroll
@@ -123,25 +169,40 @@ __global__ void __launch_bounds__(RET_COLS * RET_PARTS) retention_scan_kernel(
     }
 }
 
-// qk: float [n_tokens, qk_ld] with columns q (heads x dim) | k (heads x dim), rotated and scaled; v: the value columns
-// of the projection ([n_tokens, v_ld], head h at h * vdim); o: float [n_tokens, o_ld]; state: [slots, state_stride].
-FL_API int fl_retention_scan(const float* qk, long qk_ld, const void* v, int v_dtype, long v_ld, float* o, long o_ld,
-                             float* state, long state_stride, const float* decay, const int* req_start,
-                             const int* req_ctx, const int* req_qlen, const int* req_slot, int n_requests, int heads,
-                             int dim, int vdim, cudaStream_t stream) {
+// qkv: float [n_tokens, ld] with columns q (heads x dim) | k (heads x dim) | v (heads x vdim), q and k rotated and
+// scaled; o: float [n_tokens, o_ld]; state: [slots, state_stride].  Blocks of 16 columns instead of 32 when the
+// wider ones would leave SMs idle (a lone prompt).
+FL_API int fl_retention_scan(const float* qkv, long ld, float* o, long o_ld, float* state, long state_stride,
+                             const float* decay, const int* req_start, const int* req_ctx, const int* req_qlen,
+                             const int* req_slot, int n_requests, int heads, int dim, int vdim, int num_sms,
+                             cudaStream_t stream) {
     if (n_requests <= 0) return 0;
-    const int col_blocks = (vdim + RET_COLS - 1) / RET_COLS;
+    const bool narrow = (long)n_requests * heads * ((vdim + 31) / 32) < num_sms && vdim > 16;
+    const int cols = narrow ? 16 : 32;
+    const int col_blocks = (vdim + cols - 1) / cols;
     if (dim < 1 || dim > 256 || heads > 65535 || col_blocks > 65535) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)RET_CHUNK * (2 * dim + RET_COLS) * sizeof(float);
-    dim3 grid(n_requests, heads, col_blocks), block(RET_COLS * RET_PARTS);
+    const size_t smem = (size_t)2 * RET_CHUNK * (2 * dim + cols) * sizeof(float);
+    const int vec = dim % 4 == 0 && vdim % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qkv % 16) == 0;
+    dim3 grid(n_requests, heads, col_blocks), block(cols * RET_PARTS);
 #define FL_RET_SCAN(NI)                                                                                              \
-    FL_DISPATCH(v_dtype, T, return fl_launch(retention_scan_kernel<T, NI>, grid, block, smem, stream, qk, qk_ld,     \
-                                             (const T*)v, v_ld, o, o_ld, state, state_stride, decay, req_start,      \
-                                             req_ctx, req_qlen, req_slot, heads, dim, vdim))
-    if (dim <= 32) { FL_RET_SCAN(4); }
-    else if (dim <= 64) { FL_RET_SCAN(8); }
-    else if (dim <= 128) { FL_RET_SCAN(16); }
-    else { FL_RET_SCAN(32); }
+    {                                                                                                                \
+        if (smem > 48 * 1024) {                                                                                      \
+            cudaError_t e = narrow ? cudaFuncSetAttribute(retention_scan_kernel<NI, 16>,                             \
+                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)    \
+                                   : cudaFuncSetAttribute(retention_scan_kernel<NI, 32>,                             \
+                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+            if (e != cudaSuccess) return (int)e;                                                                     \
+        }                                                                                                            \
+        if (narrow) return fl_launch(retention_scan_kernel<NI, 16>, grid, block, smem, stream, qkv, ld, o, o_ld,     \
+                                     state, state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads,      \
+                                     dim, vdim, vec);                                                                \
+        return fl_launch(retention_scan_kernel<NI, 32>, grid, block, smem, stream, qkv, ld, o, o_ld, state,          \
+                         state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);        \
+    }
+    if (dim <= 32) FL_RET_SCAN(4)
+    else if (dim <= 64) FL_RET_SCAN(8)
+    else if (dim <= 128) FL_RET_SCAN(16)
+    else FL_RET_SCAN(32)
 #undef FL_RET_SCAN
     return 0;
 }

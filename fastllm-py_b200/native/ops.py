@@ -347,50 +347,89 @@ def diff_tc_library(dim: int, vdim: int):
 
 
 def diff_attention_tc(q, out, cache, block_table, step, heads, kv_heads, dim, vdim, window, scale, lam, eps, out_scale,
-                      page_size):
+                      page_size, include_single=True):
     """`diff_attention_simt` on the tensor cores for bfloat16: 64 rows of a request and one head per block, both
-    maps against the same staged cache rows; one build per (dim, vdim).  Prompt portions and single tokens alike."""
+    maps against the same staged cache rows; one build per (dim, vdim).  Prompt portions and, unless
+    `include_single` is False, requests that bring a single token."""
     _require_cuda(q, out, cache, block_table)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("diff_attention_tc: q, cache and out must be bfloat16")
     name, defines = diff_tc_library(dim, vdim)
     fn = _fn(name, "fl_diff_attention_tc", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int,
-                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                             c_float, c_float, c_float, c_void_p], defines)
     _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size, _ptr(block_table),
               block_table.stride(0), _ptr(step.req_start), _ptr(step.req_ctx), _ptr(step.req_qlen), step.n_requests,
-              q.shape[0], heads, kv_heads, int(window or 0), float(scale), float(lam), float(eps), float(out_scale),
+              q.shape[0], int(include_single), heads, kv_heads, int(window or 0), float(scale), float(lam), float(eps), float(out_scale),
               _stream()), "diff_attention_tc")
+
+
+DIFF_SPLIT = 128                 # keys per block of the split-key kernel for single tokens
+
+
+def diff_decode_takes(heads: int, kv_heads: int, dim: int, vdim: int) -> bool:
+    """Whether the split-key kernels for single tokens serve these sizes (groups of up to 8 query heads)."""
+    fn = load_library("diff_attention").fl_diff_decode_takes
+    fn.argtypes, fn.restype = [c_int, c_int, c_int, c_int], c_int
+    return bool(fn(heads, kv_heads, dim, vdim))
+
+
+def diff_decode(q, out, cache, block_table, tok_req, positions, decode_tokens, partial, n_splits, heads, kv_heads, dim,
+                vdim, window, scale, lam, eps, out_scale, page_size):
+    """Differential attention for the rows `decode_tokens` of q (each the single token of its request), the keys
+    shared out over `n_splits` blocks of DIFF_SPLIT keys at fixed positions, which must reach every token's last
+    key ((longest visible span - 1) // DIFF_SPLIT + 2 does); a cache row is read once for all query heads of its
+    group.  `partial`: float32, n_decode * heads * 2 * n_splits * (vdim + 2).  Other rows of `out` are left alone."""
+    _require_cuda(q, out, cache, block_table, tok_req, positions, decode_tokens, partial)
+    n = decode_tokens.numel()
+    if partial is None or partial.numel() < n * heads * 2 * n_splits * (vdim + 2):
+        raise KernelError("diff_decode: the buffer for the splits' results is too small")
+    if q.dtype != cache.dtype or out.dtype != q.dtype:
+        raise KernelError("diff_decode: q, cache and out share a dtype")
+    fn = _fn("diff_attention", "fl_diff_decode",
+             [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
+              c_void_p])
+    _check(fn(_ptr(q), dtype_code(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size,
+              _ptr(block_table), block_table.stride(0), _ptr(tok_req), _ptr(positions), _ptr(decode_tokens), n,
+              _ptr(partial), int(n_splits), heads, kv_heads, dim, vdim, int(window or 0), float(scale), float(lam),
+              float(eps), float(out_scale), _stream()), "diff_decode", 2)
 
 
 # ------------------------------------------------------------------ retention
 
-def retention_prep(proj, work, heads, dim, rot, cos, sin, positions, k_scale):
-    """proj columns q (heads x dim) | k (heads x dim) | ...: rotated (pairs (i, i + rot/2) of the first `rot`
-    dimensions), k times `k_scale`, into the float32 columns q | k of `work`."""
+def retention_prep(proj, work, heads, dim, vdim, rot, cos, sin, positions, k_scale):
+    """proj columns q (heads x dim) | k (heads x dim) | v (heads x vdim) | ...: q and k rotated (pairs (i, i + rot/2) of
+    the first `rot` dimensions), k times `k_scale`, v as it is, into the float32 columns q | k | v of `work`."""
     _require_cuda(proj, work, cos, sin, positions)
     if work.dtype != torch.float32:
         raise KernelError("retention_prep: the work buffer must be float32")
     fn = _fn("retention", "fl_retention_prep", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int,
-                                                c_void_p, c_void_p, c_void_p, c_float, c_void_p])
-    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(work), _ld(work), proj.shape[0], heads, dim, rot, _ptr(cos),
-              _ptr(sin), _ptr(positions), float(k_scale), _stream()), "retention_prep")
+                                                c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(work), _ld(work), proj.shape[0], heads, dim, vdim, rot,
+              _ptr(cos), _ptr(sin), _ptr(positions), float(k_scale), _stream()), "retention_prep")
 
 
-def retention_scan(work, proj, v_col, o, state, decay, step, heads, dim, vdim):
-    """Per request and head S <- decay S + k v^T, o = S^T q over the step's tokens; q | k are the float32 columns of
-    `work`, v the columns of `proj` from `v_col` on, `o` float32 [N, heads * vdim]; state rows [heads, vdim, dim]
-    float32 are read (unless the request starts) and written."""
-    _require_cuda(work, proj, o, state, decay)
+_sm_counts: dict = {}
+
+
+def retention_scan(work, o, state, decay, step, heads, dim, vdim):
+    """Per request and head S <- decay S + k v^T, o = S^T q over the step's tokens; q | k | v are the float32 columns
+    of `work`, `o` float32 [N, heads * vdim]; state rows [heads, vdim, dim] float32 are read (unless the request
+    starts) and written."""
+    _require_cuda(work, o, state, decay)
     if work.dtype != torch.float32 or o.dtype != torch.float32 or state.dtype != torch.float32 or \
             decay.dtype != torch.float32:
         raise KernelError("retention_scan: work, o, state and decay must be float32")
-    fn = _fn("retention", "fl_retention_scan", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_long, c_void_p,
-                                                c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                                c_int, c_int, c_void_p])
-    _check(fn(_ptr(work), _ld(work), c_void_p(proj.data_ptr() + proj.element_size() * v_col), dtype_code(proj), _ld(proj),
-              _ptr(o), _ld(o), _ptr(state), state.stride(0), _ptr(decay), _ptr(step.req_start), _ptr(step.req_ctx),
-              _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, dim, vdim, _stream()), "retention_scan")
+    sms = _sm_counts.get(work.device)
+    if sms is None:
+        sms = _sm_counts[work.device] = torch.cuda.get_device_properties(work.device).multi_processor_count
+    fn = _fn("retention", "fl_retention_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p,
+                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                c_void_p])
+    _check(fn(_ptr(work), _ld(work), _ptr(o), _ld(o), _ptr(state), state.stride(0), _ptr(decay), _ptr(step.req_start),
+              _ptr(step.req_ctx), _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, dim, vdim, sms,
+              _stream()), "retention_scan")
 
 
 def retention_gated_norm(o, proj, gate_col, out, heads, vdim, eps):

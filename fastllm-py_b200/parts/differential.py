@@ -15,8 +15,10 @@ and key/value head the two rotated key maps followed by the value
 difference and the norm are float.
 
 In bfloat16, with map and value sizes that are multiples of 16 up to 128, attention runs on the
-tensor cores (`csrc/diff_attention_tc.cu`, one build per pair of sizes); everything else, and the
-32-bit path, takes the CUDA-core kernel.
+tensor cores (`csrc/diff_attention_tc.cu`, one build per pair of sizes), and requests that bring a
+single token take a kernel that shares each token's keys out over blocks at fixed positions and
+reads a cache row once for its group of query heads (how many blocks: decided per step on the
+host, `plan_step`); everything else, and the 32-bit path, takes the CUDA-core kernel.
 """
 from __future__ import annotations
 
@@ -25,7 +27,7 @@ import math
 import torch
 
 from ..cache.needs import PagedKeysValues
-from ..native import ops
+from ..native import ops, scratch
 from .base import Part
 from .linear import Linear
 from .registry import build_part, register_part
@@ -38,6 +40,7 @@ class DifferentialAttention(Part):
     v [kv_heads * vdim, hidden], o [hidden, heads * vdim], lq1, lk1, lq2, lk2 [dim]."""
     category = "mixer"
     native_libraries = ("diff_attention",)
+    SCRATCH = "differential attention splits"
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -87,6 +90,34 @@ class DifferentialAttention(Part):
     def _tc(self) -> bool:
         return ops.diff_tc_takes(self.ctx.dtype, self.dim, self.vdim)
 
+    def _splits_keys(self) -> bool:
+        """Single tokens go to the split-key kernel (beside the tensor-core one, never in the 32-bit path, whose
+        sums keep one order whatever the cut)."""
+        if not hasattr(self, "_split_ok"):
+            self._split_ok = self._tc() and ops.diff_decode_takes(self.heads, self.kv_heads, self.dim, self.vdim)
+        return self._split_ok
+
+    # ---- what the host decides per step: how many blocks share a single token's keys
+    @property
+    def plan_key(self):
+        return ("differential_attention", self.window)
+
+    def _splits(self, longest: int) -> int:
+        span = longest if self.window is None else min(self.window, longest)
+        return (span - 1) // ops.DIFF_SPLIT + 2
+
+    def plan_step(self, step):
+        longest = step.max_seq_len
+        if step.for_graph:                                    # a captured step serves many: cover the length rounded up
+            longest = -(-longest // 1024) * 1024
+        step.plans[self.plan_key] = self._splits(longest) if step.n_decode_tokens else 0
+
+    def graph_key(self, step):
+        return step.plans.get(self.plan_key)
+
+    def _partials(self, n_tokens: int, n_splits: int):
+        return scratch.get(self.ctx.device, self.SCRATCH, n_tokens * self.heads * 2 * n_splits * (self.vdim + 2))
+
     def reserve(self, limits):
         for lin in (self.qkv, self.o):
             if lin is not None:
@@ -94,6 +125,9 @@ class DifferentialAttention(Part):
         if self.ctx.device.type == "cuda" and self._tc():
             from ..native.build import load_library
             load_library(*ops.diff_tc_library(self.dim, self.vdim))        # built now, not inside the first step
+            if self._splits_keys():                                        # sized now: nothing grows under a graph
+                longest = -(-limits.max_model_len // 1024) * 1024
+                self._partials(min(limits.max_tokens, limits.max_requests), self._splits(longest))
 
     def forward(self, h, out, step, cache):
         n = h.shape[0]
@@ -110,9 +144,19 @@ class DifferentialAttention(Part):
                       cache.slots, cache.tensor, cache.page_size)
         ctx = ws.rows("diff_ctx", n, self.heads * self.vdim, dt)
         if self._tc():
-            ops.diff_attention_tc(qkv, ctx, cache.tensor, cache.block_table, step, self.heads, self.kv_heads, self.dim,
-                                  self.vdim, self.window, self.scale, self.lam, self.norm_eps, 1.0 - self.diff,
-                                  cache.page_size)
+            split = self._splits_keys() and step.n_decode_tokens > 0
+            if not split or step.n_decode_tokens < step.n_requests:
+                ops.diff_attention_tc(qkv, ctx, cache.tensor, cache.block_table, step, self.heads, self.kv_heads,
+                                      self.dim, self.vdim, self.window, self.scale, self.lam, self.norm_eps,
+                                      1.0 - self.diff, cache.page_size, include_single=not split)
+            if split:
+                if self.plan_key not in step.plans:               # a step built by hand, not by the engine
+                    self.plan_step(step)
+                n_splits = step.plans[self.plan_key]
+                ops.diff_decode(qkv, ctx, cache.tensor, cache.block_table, step.tok_req, step.positions,
+                                step.decode_tokens, self._partials(step.n_decode_tokens, n_splits), n_splits,
+                                self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale, self.lam,
+                                self.norm_eps, 1.0 - self.diff, cache.page_size)
             return self.o.forward(ctx, out, defer=True)
         ops.diff_attention_simt(qkv, ctx, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
                                 self.kv_heads, self.dim, self.vdim, self.window, self.scale, self.lam, self.norm_eps,

@@ -87,10 +87,10 @@ class Retention(Part):
             rot = self.position.rot_dim
         else:
             cos, sin, rot = step.no_rotation, step.no_rotation, 0
-        work = ws.rows("retention_qk", n, self.qk_cols, torch.float32)
-        ops.retention_prep(proj, work, self.heads, self.dim, rot, cos, sin, step.positions, self.k_scale)
+        work = ws.rows("retention_qkv", n, self.qk_cols + self.hv, torch.float32)
+        ops.retention_prep(proj, work, self.heads, self.dim, self.vdim, rot, cos, sin, step.positions, self.k_scale)
         o = ws.rows("retention_o", n, self.hv, torch.float32)
-        ops.retention_scan(work, proj, self.qk_cols, o, cache.tensor, self.decay, step, self.heads, self.dim, self.vdim)
+        ops.retention_scan(work, o, cache.tensor, self.decay, step, self.heads, self.dim, self.vdim)
         y = ws.rows("retention_y", n, self.hv, dt)
         ops.retention_gated_norm(o, proj, self.qk_cols + self.hv, y, self.heads, self.vdim, self.norm_eps)
         return self.o.forward(y, out, defer=True)

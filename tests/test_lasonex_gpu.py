@@ -397,6 +397,27 @@ def test_tensor_core_attention_equals_the_cuda_core_one(dim, vdim, window):
     torch.cuda.synchronize()
     err = (got.float() - want.float()).abs()
     assert float(err.max()) <= 0.06 and float(err.mean()) <= 0.006, (float(err.max()), float(err.mean()))
+    # the single tokens through the split-key kernel, the portions through the tensor-core one
+    assert ops.diff_decode_takes(heads, kv_heads, dim, vdim)
+    singles = dev(torch.tensor([starts[1], starts[3]], dtype=torch.int32))
+    n_splits = (min(window or 202, 202) - 1) // ops.DIFF_SPLIT + 2
+    partial = torch.empty(2 * heads * 2 * n_splits * (vdim + 2), device="cuda")
+    both = torch.zeros_like(want)
+    ops.diff_attention_tc(dev(q), both, dev(cache), dev(bt), step, *args, include_single=False)
+    assert float(both[starts[1]].float().abs().max()) == 0.0 and float(both[starts[3]].float().abs().max()) == 0.0
+    ops.diff_decode(dev(q), both, dev(cache), dev(bt), dev(tok_req), dev(positions), singles, partial, n_splits,
+                    *args)
+    torch.cuda.synchronize()
+    err = (both.float() - want.float()).abs()
+    assert float(err.max()) <= 0.06 and float(err.mean()) <= 0.006, (float(err.max()), float(err.mean()))
+    exact = torch.empty_like(want, dtype=torch.float32)
+    ops.diff_attention_simt(dev(q).float(), exact, dev(cache).float(), dev(bt), dev(tok_req), dev(positions), *args)
+    split32 = exact.clone()
+    split32[starts[1]] = 0
+    split32[starts[3]] = 0
+    ops.diff_decode(dev(q).float(), split32, dev(cache).float(), dev(bt), dev(tok_req), dev(positions), singles, partial,
+                    n_splits, *args)
+    assert float((split32 - exact).abs().max()) <= 2e-5                    # in 32-bit the split changes the order only
     if window is not None:
         far = want.clone()
         ops.diff_attention_simt(dev(q), far, dev(cache), dev(bt), dev(tok_req), dev(positions),
