@@ -136,10 +136,16 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // silu(g) * u with the fast exponential and division: the epilogue has a fixed budget per tile (the
 // next tile's MMAs), and the exact forms cost five times the instructions for digits that a
 // bfloat16 result cannot hold (relative error about 1e-6 against bfloat16's 4e-3).
-// `act` (the same in every thread of a launch): 0 silu, 1 relu, 2 gelu in its tanh form.
-__device__ __forceinline__ float gated_act(float g, float u, int act) {
-    if (act == 1) return fmaxf(g, 0.0f) * u;
-    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+// `act` (the same in every thread of a launch; FlAct in common.cuh): silu, relu, gelu in its tanh form, or the
+// clamped swish unit with its two constants.
+__device__ __forceinline__ float gated_act(float g, float u, const FlGate act) {
+    if (act.act == FL_ACT_RELU) return fmaxf(g, 0.0f) * u;
+    if (act.act == FL_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    if (act.act == FL_ACT_CLAMPED_SWISH) {
+        g = fminf(g, act.p0);
+        u = fminf(fmaxf(u, -act.p0), act.p0);
+        return __fdividef(g, 1.0f + __expf(-act.p1 * g)) * (u + 1.0f);
+    }
     return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
@@ -217,7 +223,7 @@ template <int BN, int STAGES, typename OutT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, float* __restrict__ partial, long ld_partial, int M, int N, int K,
-    int kb_per_split, int* __restrict__ status, int gate_rows, int feat, int wp, int act) {
+    int kb_per_split, int* __restrict__ status, int gate_rows, int feat, int wp, FlGate act) {
     using L = TcSmem<BN, STAGES>;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ unsigned char smem_raw[];
@@ -641,7 +647,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, int M, int N, int K, int tiles_n, int num_tiles,
     int* __restrict__ status, int gate_rows, int splits, int kb_per_split, float* __restrict__ partial,
-    long ld_partial, const TcRope rope, int wp, int wt, int act) {
+    long ld_partial, const TcRope rope, int wp, int wt, FlGate act) {
     using L = Tc2<BNT>;
     static_assert(!GATED || BNT == 256, "the gated epilogue is written for 256-token tiles");
     static_assert(!ROPE || (!GATED && sizeof(OutT) == 2), "the rotary epilogue writes bfloat16 and is not gated");
@@ -930,7 +936,7 @@ template <int BNT, typename OutT, bool GATED = false, bool ROPE = false>
 static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M, int N,
                           int K, int num_sms, int* status, cudaStream_t stream, int gate_rows = 0, int splits = 1,
                           int kb_per_split = 0, float* partial = nullptr, long ld_partial = 0,
-                          const TcRope* rope_args = nullptr, int wp = 0, int act = 0) {
+                          const TcRope* rope_args = nullptr, int wp = 0, FlGate act = FlGate{0, 0.0f, 0.0f}) {
     static bool configured = false;
     auto kernel = gemm_tc_pair_kernel<BNT, OutT, GATED, ROPE>;
     TcRope rope = {};
@@ -1084,7 +1090,7 @@ template <int BN, int STAGES, typename OutT, bool GATED = false>
 static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc,
                      float* partial, long ld_partial, int M, int N, int K, int splits,
                      int kb_per_split, int* status, cudaStream_t stream, int gate_rows = 0, int feat = 64, int wp = 0,
-                     int act = 0) {
+                     FlGate act = FlGate{0, 0.0f, 0.0f}) {
     using L = TcSmem<BN, STAGES>;
     // This kernel is launched with programmatic overlap, so CTAs of it and of its neighbours in the stream share
     // SMs; as many of them as fit an SM by shared memory must find their tensor-memory columns free at once, or an
@@ -1301,11 +1307,12 @@ FL_API int fl_gemm_tc_partial(const void* A, long lda, const void* W, long ldw, 
 // fused kernel was launched, -1 when this problem is not taken (too few features to fill the GPU
 // without a K split, or many tokens and a plan that splits K): the caller then runs the product
 // and the activation apart.
-// (`act`: the gate's activation, 0 silu, 1 relu, 2 gelu in its tanh form.)
+// (`act_code`: the gated unit, FlAct in common.cuh, with its two constants where it has some.)
 FL_API int fl_gemm_tc_glu(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int I,
-                          int K, int act, int num_sms, int* status, cudaStream_t stream) {
+                          int K, int act_code, float act_p0, float act_p1, int num_sms, int* status, cudaStream_t stream) {
     if (M <= 0 || I <= 0) return 0;
-    if (act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+    if (act_code < 0 || act_code >= FL_ACT_COUNT) return (int)cudaErrorInvalidValue;
+    const FlGate act{act_code, act_p0, act_p1};
     if (K <= 0) return (int)cudaErrorInvalidValue;
     // Up to 128 tokens: the one-tile kernel with as few features per CTA (16 to 64 in steps of 8) as
     // still leave every CTA a place on the SMs at once (two per SM); declined when even that gives too
@@ -1342,7 +1349,7 @@ FL_API int fl_gemm_tc_glu(const void* A, long lda, const void* W, long ldw, void
 
 FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int I,
                              int K, int num_sms, int* status, cudaStream_t stream) {
-    return fl_gemm_tc_glu(A, lda, W, ldw, C, ldc, M, I, K, 0, num_sms, status, stream);
+    return fl_gemm_tc_glu(A, lda, W, ldw, C, ldc, M, I, K, 0, 0.0f, 0.0f, num_sms, status, stream);
 }
 
 // The q|k|v product of an attention layer with its rotary encoding and cache write in the epilogue (see TcRope):

@@ -69,8 +69,7 @@ __device__ __forceinline__ void ret_cp(float* dst, const float* src, int bytes) 
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-// NI: state elements per lane (dim <= 8 NI); COLS: value columns of a block.  A lane holds rows part, part + 8, ...
-// of its column.  A staged token is dim floats of q, dim of k and COLS of v.
+// NI: state elements per lane (dim <= 8 NI, a multiple of 4); COLS: value columns of a block.  A staged token is dim floats of q, dim of k and COLS of v.
 template <int NI, int COLS>
 __global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
     const float* __restrict__ qkv, long ld, float* __restrict__ o, long o_ld, float* __restrict__ state,
@@ -86,11 +85,13 @@ __global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
     const int start = req_start[r], qlen = req_qlen[r];
     const bool live = col < vdim;
     float* srow = state + (long)req_slot[r] * state_stride + ((long)h * vdim + (live ? col : 0)) * dim;
+    // lane `part` holds, of its column, rows (i / 4) * 32 + part * 4 + i % 4: four neighbours at a time, so that the
+    // eight lanes of a column read 128 consecutive bytes of a staged q or k row with one 16-byte load each
     float S[NI];
     const bool fresh = req_ctx[r] == 0;
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
-        const int d = part + i * RET_PARTS;
+        const int d = (i >> 2) * 32 + part * 4 + (i & 3);
         S[i] = (!fresh && live && d < dim) ? srow[d] : 0.0f;
     }
     const float g = decay[h];
@@ -146,11 +147,25 @@ __global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
             const float vj = live ? qs[2 * dim + (tid >> 3)] : 0.0f;
             float acc = 0.0f;
 #pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                const int d = part + i * RET_PARTS;
-                if (d < dim) {
-                    S[i] = g * S[i] + ks[d] * vj;
-                    acc += S[i] * qs[d];
+            for (int i4 = 0; i4 < NI / 4; ++i4) {
+                const int d0 = i4 * 32 + part * 4;
+                float kk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (vec) {                                 // dim is a multiple of 4: four rows are inside or outside together
+                    if (d0 < dim) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(ks + d0);
+                        const float4 q4 = *reinterpret_cast<const float4*>(qs + d0);
+                        kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
+                        qq[0] = q4.x; qq[1] = q4.y; qq[2] = q4.z; qq[3] = q4.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (d0 + e < dim) { kk[e] = ks[d0 + e]; qq[e] = qs[d0 + e]; }
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {              // (rows beyond dim hold zeros and add nothing)
+                    S[i4 * 4 + e] = g * S[i4 * 4 + e] + kk[e] * vj;
+                    acc += S[i4 * 4 + e] * qq[e];
                 }
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -163,7 +178,7 @@ __global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
     if (live) {
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
-            const int d = part + i * RET_PARTS;
+            const int d = (i >> 2) * 32 + part * 4 + (i & 3);
             if (d < dim) srow[d] = S[i];
         }
     }

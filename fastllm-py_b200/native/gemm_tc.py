@@ -29,7 +29,7 @@ def _lib():
                                             ctypes.POINTER(c_int)]
         lib.fl_gemm_tc_plan_for.restype = None
         lib.fl_gemm_tc_glu.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
-                                       c_int, c_int, c_int, c_void_p, c_void_p]
+                                       c_int, c_int, ctypes.c_float, ctypes.c_float, c_int, c_void_p, c_void_p]
         lib.fl_gemm_tc_glu.restype = c_int
         lib.fl_gemm_tc_qkv_rope.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -254,11 +254,9 @@ def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
 
 def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor, activation: str = "silu", params=(0.0, 0.0)) -> bool:
     """out[M, I] = act(a @ gate^T) * (a @ up^T) for w = [gate; up] stacked as [2 I, K], all
-    bfloat16, in one kernel (the activation in the product's epilogue; silu, relu or gelu_tanh).
+    bfloat16, in one kernel (the gated unit in the product's epilogue: `ops.ACTIVATIONS`, with its `params`).
     Returns False, having done nothing, when the kernel does not take the problem (its plan splits K)."""
-    if ops.activation_code(activation) > 2:                 # units with constants of their own: product, then ops.glu
-        return False
-    key = ("glu", activation, a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, out.data_ptr(), out.shape,
+    key = ("glu", activation, tuple(params), a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, out.data_ptr(), out.shape,
            out.stride(0), out.dtype)
     known = _launches.get(key)                              # (see gemm)
     if known is not None:
@@ -283,7 +281,7 @@ def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor, activation: str = "silu",
         return False
     fn = _lib().fl_gemm_tc_glu
     args = (ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops._ld(out), m, inter, k, ops.activation_code(activation),
-            _num_sms(a.device), ops._ptr(status_word(a.device)))
+            float(params[0]), float(params[1]), _num_sms(a.device), ops._ptr(status_word(a.device)))
     rc = fn(*args, ops._stream())
     if rc == -1:
         _remember(key, False)

@@ -423,3 +423,25 @@ def test_tensor_core_attention_equals_the_cuda_core_one(dim, vdim, window):
         ops.diff_attention_simt(dev(q), far, dev(cache), dev(bt), dev(tok_req), dev(positions),
                                 *(args[:4] + (window - 1,) + args[5:]))
         assert float((far[60].float() - want[60].float()).abs().max()) > 0.3         # the edge key decides row 60
+
+
+def test_clamped_unit_in_the_tensor_core_products_epilogue():
+    """The gated tcgen05 product with the clamped swish unit against the product and the unit apart, in its
+    one-tile form (a decode-sized step) and its CTA-pair form (a prompt-sized step); limits small enough to bite."""
+    from fastllm_py_b200.native import gemm_tc
+
+    torch.manual_seed(6)
+    taken = 0
+    for m, inter, k, limit in ((48, 1536, 256, 0.7), (2048, 4096, 512, 1.2)):
+        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(2 * inter, k, device="cuda") * k ** -0.5).to(torch.bfloat16)
+        out = torch.zeros(m, inter, device="cuda", dtype=torch.bfloat16)
+        if not gemm_tc.gemm_swiglu(a, w, out, "clamped_swish", (limit, 1.702)):
+            continue
+        taken += 1
+        prod = a.float() @ w.float().T
+        g, u = prod[:, :inter].clamp(max=limit), prod[:, inter:].clamp(-limit, limit)
+        ref = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+        assert float((g == limit).float().mean()) > 0.05                  # the limit is reached often
+        assert float((out.float() - ref).abs().max()) <= 0.03 * float(ref.abs().max()) + 1e-2, m
+    assert taken >= 1
