@@ -9,8 +9,8 @@
 //
 // A cache page is [kv_heads, page_size, 2 dim + vdim]: a token's two key maps, then its value.
 //
-//   diff_prep            per (token, head): rotates the query maps in place; rotates the key maps
-//                        into the token's cache row and copies the value behind them
+//   diff_prep            per token: rotates the query maps in place; rotates the key maps into the
+//                        token's cache rows and copies the values behind them
 //   diff_attention_simt  per (token, query head): CUDA cores, any sizes, bfloat16 or true 32-bit;
 //                        key tiles start at multiples of 128 of the absolute position, so every sum's
 //                        order depends on the token's own position only (cuts and batches agree bit
@@ -26,51 +26,54 @@
 
 #define DIFF_TILE 128
 
+// One block per token.
 template <typename T>
-__global__ void __launch_bounds__(128) diff_prep_kernel(
+__global__ void __launch_bounds__(256) diff_prep_kernel(
     T* __restrict__ proj, long ld, int heads, int kv_heads, int dim, int vdim, int rot,
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, const int* __restrict__ positions,
     const int* __restrict__ slots, T* __restrict__ cache, long page_stride, int page_size) {
     pdl_wait();
     pdl_trigger();
-    const int t = blockIdx.x, unit = blockIdx.y;
+    const int t = blockIdx.x;
     const int half = rot >> 1;
     const long pos = positions[t];
     const float* cs = cos_table + pos * half;
     const float* sn = sin_table + pos * half;
     T* row = proj + (long)t * ld;
-    if (unit < heads) {                                    // both maps of a query head, in place
-        T* x = row + (long)unit * 2 * dim;
-        for (int i = threadIdx.x; i < 2 * half; i += blockDim.x) {
-            const int m = i / half, j = i - m * half;
-            T* xm = x + m * dim;
-            const float a = to_f32<T>(xm[j]), b = to_f32<T>(xm[j + half]);
-            xm[j] = from_f32<T>(a * cs[j] - b * sn[j]);
-            xm[j + half] = from_f32<T>(b * cs[j] + a * sn[j]);
-        }
-        return;
+    for (int i = threadIdx.x; i < heads * 2 * half; i += blockDim.x) {        // every map of every query head, in place
+        const int map = i / half, j = i - map * half;
+        T* xm = row + (long)map * dim;
+        const float a = to_f32<T>(xm[j]), b = to_f32<T>(xm[j + half]);
+        xm[j] = from_f32<T>(a * cs[j] - b * sn[j]);
+        xm[j + half] = from_f32<T>(b * cs[j] + a * sn[j]);
     }
     if (cache == nullptr) return;
     const int slot = slots[t];
     if (slot < 0) return;
-    const int g = unit - heads;
     const long page = slot / page_size;
     const int off = slot - (int)page * page_size;
     const int row_w = 2 * dim + vdim;
-    T* dst = cache + page * page_stride + ((long)g * page_size + off) * row_w;
-    const T* k = row + (long)heads * 2 * dim + (long)g * 2 * dim;
-    const T* v = row + (long)(heads + kv_heads) * 2 * dim + (long)g * vdim;
-    for (int i = threadIdx.x; i < 2 * half; i += blockDim.x) {
-        const int m = i / half, j = i - m * half;
-        const float a = to_f32<T>(k[m * dim + j]), b = to_f32<T>(k[m * dim + j + half]);
-        dst[m * dim + j] = from_f32<T>(a * cs[j] - b * sn[j]);
-        dst[m * dim + j + half] = from_f32<T>(b * cs[j] + a * sn[j]);
+    T* dst = cache + page * page_stride + (long)off * row_w;                   // head g's row: + g * page_size * row_w
+    const long head_stride = (long)page_size * row_w;
+    const T* k = row + (long)heads * 2 * dim;
+    const T* v = k + (long)kv_heads * 2 * dim;
+    for (int i = threadIdx.x; i < kv_heads * 2 * half; i += blockDim.x) {
+        const int map = i / half, j = i - map * half;                          // map = 2 g + (0 | 1)
+        const T* km = k + (long)map * dim;
+        T* dm = dst + (map >> 1) * head_stride + (map & 1) * dim;
+        const float a = to_f32<T>(km[j]), b = to_f32<T>(km[j + half]);
+        dm[j] = from_f32<T>(a * cs[j] - b * sn[j]);
+        dm[j + half] = from_f32<T>(b * cs[j] + a * sn[j]);
     }
-    for (int i = threadIdx.x; i < 2 * (dim - rot); i += blockDim.x) {
-        const int m = i / (dim - rot), j = rot + i - m * (dim - rot);
-        dst[m * dim + j] = k[m * dim + j];
+    const int rest = dim - rot;
+    for (int i = threadIdx.x; i < kv_heads * 2 * rest; i += blockDim.x) {
+        const int map = i / rest, j = rot + i - map * rest;
+        dst[(map >> 1) * head_stride + (map & 1) * dim + j] = k[(long)map * dim + j];
     }
-    for (int i = threadIdx.x; i < vdim; i += blockDim.x) dst[2 * dim + i] = v[i];
+    for (int i = threadIdx.x; i < kv_heads * vdim; i += blockDim.x) {
+        const int g = i / vdim, j = i - g * vdim;
+        dst[g * head_stride + 2 * dim + j] = v[i];
+    }
 }
 
 // proj: [n_tokens, ld] with columns q (heads x 2 x dim) | k (kv_heads x 2 x dim) | v (kv_heads x vdim);
@@ -79,10 +82,9 @@ FL_API int fl_diff_prep(void* proj, int dtype, long ld, int n_tokens, int heads,
                         const float* cos_table, const float* sin_table, const int* positions, const int* slots,
                         void* cache, long page_stride, int page_size, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (rot < 0 || rot > dim || (rot & 1) || heads + kv_heads > 65535) return (int)cudaErrorInvalidValue;
-    dim3 grid(n_tokens, heads + kv_heads);
-    FL_DISPATCH(dtype, T, return fl_launch(diff_prep_kernel<T>, grid, dim3(128), 0, stream, (T*)proj, ld, heads, kv_heads,
-                                           dim, vdim, rot, cos_table, sin_table, positions, slots, (T*)cache,
+    if (rot < 0 || rot > dim || (rot & 1)) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(dtype, T, return fl_launch(diff_prep_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)proj, ld, heads,
+                                           kv_heads, dim, vdim, rot, cos_table, sin_table, positions, slots, (T*)cache,
                                            page_stride, page_size));
     return 0;
 }
@@ -200,6 +202,21 @@ FL_API int fl_diff_attention_simt(const void* q, int dtype, long q_ld, void* out
 // ------------------------------------------------------------------ single tokens, keys split over blocks
 #define DIFF_SPLIT 128           // keys of a split: one per thread
 
+__device__ __forceinline__ void load8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
 // GROUP: query heads per key/value head, rounded up to a power of two (at most 8); pair hm = 2 * head in group + map.
 // partial: [n_decode][heads][2 maps][n_splits][vdim + 2] floats: maximum, sum, weighted values.
 template <typename T, int GROUP>
@@ -207,7 +224,7 @@ __global__ void __launch_bounds__(DIFF_SPLIT) diff_decode_kernel(
     const T* __restrict__ q, long q_ld, const T* __restrict__ cache, long page_stride, int page_size,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req, const int* __restrict__ positions,
     const int* __restrict__ decode_tokens, float* __restrict__ partial, int n_splits, int heads, int kv_heads, int dim,
-    int vdim, int window, float scale) {
+    int vdim, int window, float scale, int vec8) {
     pdl_wait();
     pdl_trigger();
     constexpr int GM = 2 * GROUP;
@@ -244,14 +261,30 @@ __global__ void __launch_bounds__(DIFF_SPLIT) diff_decode_kernel(
         const long off = (long)bt[j / page_size] * page_stride + ((long)g * page_size + j % page_size) * row_w;
         off_s[tid] = off + 2 * dim;
         const T* kp = cache + off;
-        for (int d = 0; d < dim; ++d) {
-            const float k1 = to_f32<T>(kp[d]), k2 = to_f32<T>(kp[dim + d]);
+        if (vec8) {                                                   // eight elements of both maps per load
+            for (int d = 0; d < dim; d += 8) {
+                float k1[8], k2[8];
+                load8(kp + d, k1);
+                load8(kp + dim + d, k2);
 #pragma unroll
-            for (int hh = 0; hh < GROUP; ++hh)
-                if (hh < group) {
-                    s[2 * hh] += q_s[(2 * hh) * dim + d] * k1;
-                    s[2 * hh + 1] += q_s[(2 * hh + 1) * dim + d] * k2;
-                }
+                for (int e = 0; e < 8; ++e)
+#pragma unroll
+                    for (int hh = 0; hh < GROUP; ++hh)
+                        if (hh < group) {
+                            s[2 * hh] += q_s[(2 * hh) * dim + d + e] * k1[e];
+                            s[2 * hh + 1] += q_s[(2 * hh + 1) * dim + d + e] * k2[e];
+                        }
+            }
+        } else {
+            for (int d = 0; d < dim; ++d) {
+                const float k1 = to_f32<T>(kp[d]), k2 = to_f32<T>(kp[dim + d]);
+#pragma unroll
+                for (int hh = 0; hh < GROUP; ++hh)
+                    if (hh < group) {
+                        s[2 * hh] += q_s[(2 * hh) * dim + d] * k1;
+                        s[2 * hh + 1] += q_s[(2 * hh + 1) * dim + d] * k2;
+                    }
+            }
         }
     }
     const int warp = tid >> 5, lane = tid & 31;
@@ -286,6 +319,7 @@ __global__ void __launch_bounds__(DIFF_SPLIT) diff_decode_kernel(
         float acc[GM];
 #pragma unroll
         for (int hm = 0; hm < GM; ++hm) acc[hm] = 0.0f;
+#pragma unroll 8
         for (int jj = j_begin; jj < j_end; ++jj) {
             const float v = to_f32<T>(cache[off_s[jj] + d]);
 #pragma unroll
@@ -365,12 +399,14 @@ FL_API int fl_diff_decode(const void* q, int dtype, long q_ld, void* out, long o
     const int gp = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
     const size_t smem = (size_t)DIFF_SPLIT * (sizeof(long) + 2 * gp * sizeof(float)) + (size_t)(8 * gp + 2 * gp * dim) * sizeof(float);
     dim3 grid(n_decode, kv_heads, n_splits);
+    // (rows start 16 bytes aligned when the row and page sizes are multiples of 8 elements and the pool is aligned)
+    const int vec8 = dim % 8 == 0 && vdim % 8 == 0 && page_stride % 8 == 0 && ((uintptr_t)cache % 32) == 0;
     int rc = 0;
 #define FL_DIFF_DECODE(G)                                                                                            \
     FL_DISPATCH(dtype, T, rc = fl_launch(diff_decode_kernel<T, G>, grid, dim3(DIFF_SPLIT), smem, stream, (const T*)q, \
                                          q_ld, (const T*)cache, page_stride, page_size, block_table, bt_stride,      \
                                          tok_req, positions, decode_tokens, partial, n_splits, heads, kv_heads, dim, \
-                                         vdim, window, scale))
+                                         vdim, window, scale, vec8))
     if (gp == 1) { FL_DIFF_DECODE(1); }
     else if (gp == 2) { FL_DIFF_DECODE(2); }
     else if (gp == 4) { FL_DIFF_DECODE(4); }

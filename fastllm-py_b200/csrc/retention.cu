@@ -6,7 +6,7 @@
 // `k_scale` after the rotation.  The head's o is divided by its root mean square and multiplied by
 // silu(gate).
 //
-//   retention_prep        per (token, q, k or v head): rotation and scale into a float work row q | k | v
+//   retention_prep        per token: rotation and scale of every head into a float work row q | k | v
 //   retention_scan        per (request, head, 32 or 16 value columns): the recurrence over the portion's tokens,
 //                         one value column's state spread over eight lanes' registers, the tokens' q, k and
 //                         v staged through shared memory a chunk of 16 ahead (cp.async, two buffers)
@@ -18,37 +18,39 @@
 // projections is float.
 #include "common.cuh"
 
-#define RET_PARTS 8              // lanes that share one value column
-#define RET_COLS 32              // value columns of a block
 #define RET_CHUNK 16             // tokens staged at a time
 
+// One block per token: the rotated pairs of every q and k head, what lies behind them, and the values.
 template <typename T>
-__global__ void __launch_bounds__(128) retention_prep_kernel(
+__global__ void __launch_bounds__(256) retention_prep_kernel(
     const T* __restrict__ proj, long ld, float* __restrict__ work, long work_ld, int heads, int dim, int vdim, int rot,
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, const int* __restrict__ positions,
     float k_scale) {
     pdl_wait();
     pdl_trigger();
-    const int t = blockIdx.x, unit = blockIdx.y;           // units: q heads, k heads, v heads, in the projection's order
-    if (unit >= 2 * heads) {                               // a value head: widened to float as it is
-        const long off = (long)2 * heads * dim + (long)(unit - 2 * heads) * vdim;
-        for (int j = threadIdx.x; j < vdim; j += blockDim.x)
-            work[(long)t * work_ld + off + j] = to_f32<T>(proj[(long)t * ld + off + j]);
-        return;
-    }
+    const int t = blockIdx.x;
     const int half = rot >> 1;
     const long pos = positions[t];
     const float* cs = cos_table + pos * half;
     const float* sn = sin_table + pos * half;
-    const T* x = proj + (long)t * ld + (long)unit * dim;
-    float* y = work + (long)t * work_ld + (long)unit * dim;
-    const float f = unit < heads ? 1.0f : k_scale;
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        const float a = to_f32<T>(x[j]), b = to_f32<T>(x[j + half]);
-        y[j] = (a * cs[j] - b * sn[j]) * f;
-        y[j + half] = (b * cs[j] + a * sn[j]) * f;
+    const T* x = proj + (long)t * ld;
+    float* y = work + (long)t * work_ld;
+    for (int i = threadIdx.x; i < 2 * heads * half; i += blockDim.x) {
+        const int unit = i / half, j = i - unit * half;     // units: q heads, then k heads, in the projection's order
+        const float f = unit < heads ? 1.0f : k_scale;
+        const long at = (long)unit * dim + j;
+        const float a = to_f32<T>(x[at]), b = to_f32<T>(x[at + half]);
+        y[at] = (a * cs[j] - b * sn[j]) * f;
+        y[at + half] = (b * cs[j] + a * sn[j]) * f;
     }
-    for (int j = rot + threadIdx.x; j < dim; j += blockDim.x) y[j] = to_f32<T>(x[j]) * f;
+    const int rest = dim - rot;
+    for (int i = threadIdx.x; i < 2 * heads * rest; i += blockDim.x) {
+        const int unit = i / rest;
+        const long at = (long)unit * dim + rot + (i - unit * rest);
+        y[at] = to_f32<T>(x[at]) * (unit < heads ? 1.0f : k_scale);
+    }
+    const long v0 = (long)2 * heads * dim;
+    for (int i = threadIdx.x; i < heads * vdim; i += blockDim.x) y[v0 + i] = to_f32<T>(x[v0 + i]);   // widened as they are
 }
 
 // proj columns: q (heads x dim) | k (heads x dim) | v (heads x vdim) | ...; work columns: q | k | v (float).
@@ -56,8 +58,8 @@ FL_API int fl_retention_prep(const void* proj, int dtype, long ld, float* work, 
                              int dim, int vdim, int rot, const float* cos_table, const float* sin_table,
                              const int* positions, float k_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (rot < 0 || rot > dim || (rot & 1) || 3 * heads > 65535) return (int)cudaErrorInvalidValue;
-    FL_DISPATCH(dtype, T, return fl_launch(retention_prep_kernel<T>, dim3(n_tokens, 3 * heads), dim3(128), 0, stream,
+    if (rot < 0 || rot > dim || (rot & 1)) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(dtype, T, return fl_launch(retention_prep_kernel<T>, dim3(n_tokens), dim3(256), 0, stream,
                                            (const T*)proj, ld, work, work_ld, heads, dim, vdim, rot, cos_table,
                                            sin_table, positions, k_scale));
     return 0;
@@ -69,9 +71,10 @@ __device__ __forceinline__ void ret_cp(float* dst, const float* src, int bytes) 
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-// NI: state elements per lane (dim <= 8 NI, a multiple of 4); COLS: value columns of a block.  A staged token is dim floats of q, dim of k and COLS of v.
-template <int NI, int COLS>
-__global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
+// PARTS: lanes that share one value column (8 or 16); NI: state elements per lane (dim <= PARTS * NI, a multiple
+// of 4); COLS: value columns of a block.  A staged token is dim floats of q, dim of k and COLS of v.
+template <int NI, int COLS, int PARTS>
+__global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
     const float* __restrict__ qkv, long ld, float* __restrict__ o, long o_ld, float* __restrict__ state,
     long state_stride, const float* __restrict__ decay, const int* __restrict__ req_start,
     const int* __restrict__ req_ctx, const int* __restrict__ req_qlen, const int* __restrict__ req_slot, int heads,
@@ -81,17 +84,17 @@ __global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
     extern __shared__ __align__(16) float ret_smem[];      // two buffers of [CHUNK][2 dim + COLS]
     const int row_w = 2 * dim + COLS;
     const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
-    const int tid = threadIdx.x, part = tid & (RET_PARTS - 1), col = col0 + (tid >> 3);
+    const int tid = threadIdx.x, part = tid % PARTS, col = col0 + tid / PARTS;
     const int start = req_start[r], qlen = req_qlen[r];
     const bool live = col < vdim;
     float* srow = state + (long)req_slot[r] * state_stride + ((long)h * vdim + (live ? col : 0)) * dim;
-    // lane `part` holds, of its column, rows (i / 4) * 32 + part * 4 + i % 4: four neighbours at a time, so that the
-    // eight lanes of a column read 128 consecutive bytes of a staged q or k row with one 16-byte load each
+    // lane `part` holds, of its column, rows (i / 4) * 4 PARTS + part * 4 + i % 4: four neighbours at a time, so that
+    // the lanes of a column read consecutive bytes of a staged q or k row with one 16-byte load each
     float S[NI];
     const bool fresh = req_ctx[r] == 0;
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
-        const int d = (i >> 2) * 32 + part * 4 + (i & 3);
+        const int d = (i >> 2) * (4 * PARTS) + part * 4 + (i & 3);
         S[i] = (!fresh && live && d < dim) ? srow[d] : 0.0f;
     }
     const float g = decay[h];
@@ -144,11 +147,11 @@ __global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
         for (int c = 0; c < n; ++c) {
             const float* qs = rows + c * row_w;
             const float* ks = qs + dim;
-            const float vj = live ? qs[2 * dim + (tid >> 3)] : 0.0f;
+            const float vj = live ? qs[2 * dim + tid / PARTS] : 0.0f;
             float acc = 0.0f;
 #pragma unroll
             for (int i4 = 0; i4 < NI / 4; ++i4) {
-                const int d0 = i4 * 32 + part * 4;
+                const int d0 = i4 * (4 * PARTS) + part * 4;
                 float kk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 if (vec) {                                 // dim is a multiple of 4: four rows are inside or outside together
                     if (d0 < dim) {
@@ -171,6 +174,7 @@ __global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (PARTS == 16) acc += __shfl_xor_sync(0xffffffffu, acc, 8);
             if (part == 0 && live) o[(long)(start + base + c) * o_ld + (long)h * vdim + col] = acc;
         }
         __syncthreads();                                   // the buffer is staged into again next round
@@ -178,48 +182,58 @@ __global__ void __launch_bounds__(COLS * RET_PARTS) retention_scan_kernel(
     if (live) {
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
-            const int d = (i >> 2) * 32 + part * 4 + (i & 3);
+            const int d = (i >> 2) * (4 * PARTS) + part * 4 + (i & 3);
             if (d < dim) srow[d] = S[i];
         }
     }
 }
 
+template <int NI, int COLS, int PARTS>
+static int launch_ret_scan(dim3 grid, size_t smem, cudaStream_t stream, const float* qkv, long ld, float* o, long o_ld,
+                           float* state, long state_stride, const float* decay, const int* req_start, const int* req_ctx,
+                           const int* req_qlen, const int* req_slot, int heads, int dim, int vdim, int vec) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(retention_scan_kernel<NI, COLS, PARTS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return fl_launch(retention_scan_kernel<NI, COLS, PARTS>, grid, dim3(COLS * PARTS), smem, stream, qkv, ld, o, o_ld,
+                     state, state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);
+}
+
 // qkv: float [n_tokens, ld] with columns q (heads x dim) | k (heads x dim) | v (heads x vdim), q and k rotated and
-// scaled; o: float [n_tokens, o_ld]; state: [slots, state_stride].  Blocks of 16 columns instead of 32 when the
-// wider ones would leave SMs idle (a lone prompt).
+// scaled; o: float [n_tokens, o_ld]; state: [slots, state_stride].  Blocks of 32 columns with eight lanes a column;
+// when those would leave SMs idle (a lone prompt), blocks of 16 columns, with sixteen lanes a column for keys of
+// 64 and more, so that twice the warps share a token's chain.
 FL_API int fl_retention_scan(const float* qkv, long ld, float* o, long o_ld, float* state, long state_stride,
                              const float* decay, const int* req_start, const int* req_ctx, const int* req_qlen,
                              const int* req_slot, int n_requests, int heads, int dim, int vdim, int num_sms,
                              cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     const bool narrow = (long)n_requests * heads * ((vdim + 31) / 32) < num_sms && vdim > 16;
+    const bool wide = narrow && dim >= 64;                   // sixteen lanes a column
     const int cols = narrow ? 16 : 32;
     const int col_blocks = (vdim + cols - 1) / cols;
     if (dim < 1 || dim > 256 || heads > 65535 || col_blocks > 65535) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)2 * RET_CHUNK * (2 * dim + cols) * sizeof(float);
     const int vec = dim % 4 == 0 && vdim % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qkv % 16) == 0;
-    dim3 grid(n_requests, heads, col_blocks), block(cols * RET_PARTS);
-#define FL_RET_SCAN(NI)                                                                                              \
-    {                                                                                                                \
-        if (smem > 48 * 1024) {                                                                                      \
-            cudaError_t e = narrow ? cudaFuncSetAttribute(retention_scan_kernel<NI, 16>,                             \
-                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)    \
-                                   : cudaFuncSetAttribute(retention_scan_kernel<NI, 32>,                             \
-                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-            if (e != cudaSuccess) return (int)e;                                                                     \
-        }                                                                                                            \
-        if (narrow) return fl_launch(retention_scan_kernel<NI, 16>, grid, block, smem, stream, qkv, ld, o, o_ld,     \
-                                     state, state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads,      \
-                                     dim, vdim, vec);                                                                \
-        return fl_launch(retention_scan_kernel<NI, 32>, grid, block, smem, stream, qkv, ld, o, o_ld, state,          \
-                         state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);        \
+    dim3 grid(n_requests, heads, col_blocks);
+#define FL_RET_ARGS grid, smem, stream, qkv, ld, o, o_ld, state, state_stride, decay, req_start, req_ctx, req_qlen, \
+                    req_slot, heads, dim, vdim, vec
+    if (wide) {
+        if (dim <= 64) return launch_ret_scan<4, 16, 16>(FL_RET_ARGS);
+        if (dim <= 128) return launch_ret_scan<8, 16, 16>(FL_RET_ARGS);
+        return launch_ret_scan<16, 16, 16>(FL_RET_ARGS);
     }
-    if (dim <= 32) FL_RET_SCAN(4)
-    else if (dim <= 64) FL_RET_SCAN(8)
-    else if (dim <= 128) FL_RET_SCAN(16)
-    else FL_RET_SCAN(32)
-#undef FL_RET_SCAN
-    return 0;
+    if (narrow) {
+        if (dim <= 32) return launch_ret_scan<4, 16, 8>(FL_RET_ARGS);
+        return launch_ret_scan<8, 16, 8>(FL_RET_ARGS);
+    }
+    if (dim <= 32) return launch_ret_scan<4, 32, 8>(FL_RET_ARGS);
+    if (dim <= 64) return launch_ret_scan<8, 32, 8>(FL_RET_ARGS);
+    if (dim <= 128) return launch_ret_scan<16, 32, 8>(FL_RET_ARGS);
+    return launch_ret_scan<32, 32, 8>(FL_RET_ARGS);
+#undef FL_RET_ARGS
 }
 
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]); one warp per (token, head).
