@@ -5,7 +5,8 @@
 // its value (k1 | k2 | v, DIFF_VDIM the last).  Per head, with a_m = softmax(q_m . k_m * scale) V:
 //     o = a_1 - lambda a_2;   out = o / sqrt(mean(o^2) + eps) * out_scale
 //
-// A CTA of four warps takes 64 consecutive query rows of one request and one query head and walks the
+// A CTA of eight warps (four per map, 16 rows each) takes 64 consecutive query rows of one request and one query
+// head and walks the
 // request's keys in blocks of 64, from the first key any of its rows may see to the last, through the
 // block table: rows cached by earlier steps and the rows this step wrote are read alike, so a portion
 // of a prompt is the same as a whole prompt, and a single decoded token is a tile of one row (warps
@@ -14,8 +15,10 @@
 // the partial maxima and sums a row goes through depend on the row's position only.  A block's rows
 // (both key maps and the value: one piece of memory per token) come by cp.async into a two-stage ring
 // while the block before is multiplied; both maps are multiplied against the same staged values, each
-// with a running maximum and sum of its own, and meet only in the epilogue, where the row's mean
-// square is summed over the four lanes that hold it.  Probabilities are rounded to bfloat16 only as
+// by its own four warps with a running maximum and sum of its own (half the accumulators per thread,
+// twice the warps an SM holds), and meet only in the epilogue: the second map's warps leave their
+// normalised rows in shared memory, the first map's take the difference, sum the row's mean square over
+// the four lanes that hold it and store.  Probabilities are rounded to bfloat16 only as
 // the operand of P V.
 //
 // DIFF_DIM and DIFF_VDIM are compile-time constants, multiples of 16 up to 128.
@@ -29,7 +32,7 @@
 #endif
 #define DTC_BM 64
 #define DTC_BN 64
-#define DTC_THREADS 128
+#define DTC_THREADS 256
 #define DTC_ROW (2 * DIFF_DIM + DIFF_VDIM)    // elements of a cache row
 #define DTC_KP (DTC_ROW + 8)                  // padded pitches in shared memory: ldmatrix without bank conflicts
 #define DTC_QP (2 * DIFF_DIM + 8)
@@ -66,7 +69,7 @@ __device__ __forceinline__ uint32_t dtc_pack(float lo, float hi) {
 }
 __device__ __forceinline__ float dtc_weight(float a, float b) { return (a == -CUDART_INF_F) ? 0.0f : exp2f(a - b); }
 
-__global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
+__global__ void __launch_bounds__(DTC_THREADS, 2) diff_attention_tc_kernel(
     const bf16* __restrict__ q, long q_ld, bf16* __restrict__ out, long out_ld, const bf16* __restrict__ cache,
     long page_stride, int page_size, int page_shift, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ req_start, const int* __restrict__ req_ctx, const int* __restrict__ req_qlen,
@@ -99,7 +102,9 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
     const int lo_tile = window > 0 ? max(0, pos_first - window + 1) : 0;
     const int kb_begin = lo_tile / DTC_BN, kb_end = pos_last / DTC_BN + 1;
     const int* bt = block_table + (long)req * bt_stride;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int m = tid >> 7;                                            // this warp's map
+    const int warp = (tid >> 5) & 3;                                   // which 16 rows of the tile
     const bool has_rows = warp * 16 < rows_here;                       // a warp without rows only loads
 
     constexpr int Q_CHUNKS = 2 * DIFF_DIM / 8, R_CHUNKS = DTC_ROW / 8;
@@ -111,10 +116,10 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
             dtc_cp16(Qs + r * DTC_QP + ch * 8, src, real);
         }
     };
-    // Two threads per token row, half of the row's chunks each: one page lookup per thread and block.
+    // Four threads per token row, a quarter of the row's chunks each: one page lookup per thread and block.
     auto load_rows = [&](int kb, int stage) {
         bf16* dst = Rs + stage * DTC_BN * DTC_KP;
-        const int r = tid >> 1;
+        const int r = tid >> 2;
         const int j = kb * DTC_BN + r;
         const bool real = j >= lo_tile && j <= pos_last;
         long a = 0;
@@ -123,18 +128,16 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
             const int off = page_shift >= 0 ? (j & (page_size - 1)) : (j - pg * page_size);
             a = (long)bt[pg] * page_stride + ((long)kvh * page_size + off) * DTC_ROW;
         }
-        for (int ch = (tid & 1); ch < R_CHUNKS; ch += 2) dtc_cp16(dst + r * DTC_KP + ch * 8, cache + a + ch * 8, real);
+        for (int ch = (tid & 3); ch < R_CHUNKS; ch += 4) dtc_cp16(dst + r * DTC_KP + ch * 8, cache + a + ch * 8, real);
     };
 
-    float o_acc[2][DIFF_VDIM / 8][4];
+    float o_acc[DIFF_VDIM / 8][4];
 #pragma unroll
-    for (int m = 0; m < 2; ++m)
+    for (int i = 0; i < DIFF_VDIM / 8; ++i)
 #pragma unroll
-        for (int i = 0; i < DIFF_VDIM / 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o_acc[m][i][j] = 0.0f;
-    float m_run[2][2] = {{-CUDART_INF_F, -CUDART_INF_F}, {-CUDART_INF_F, -CUDART_INF_F}};
-    float l_run[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+        for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.0f;
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};
+    float l_run[2] = {0.0f, 0.0f};
     const int g = lane >> 2, tq = lane & 3;
     const int pos_row[2] = {ctx + row0 + warp * 16 + g, ctx + row0 + warp * 16 + g + 8};
 
@@ -158,8 +161,7 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
         // a block none of this warp's rows can see (the tile's rows are 64 positions apart at most, a warp's 16)
         const bool none_seen = kb * DTC_BN > warp_pos_hi || (window > 0 && kb * DTC_BN + DTC_BN - 1 <= warp_pos_lo - window);
         if (has_rows && !none_seen) {
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
+            {
                 // ---- S = Q_m K_m^T for this warp's 16 rows and the block's 64 keys
                 float s[DTC_BN / 8][4];
 #pragma unroll
@@ -201,26 +203,26 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
                 for (int r = 0; r < 2; ++r) {
                     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                    const float m_new = fmaxf(m_run[m][r], mx[r]);
-                    corr[r] = dtc_weight(m_run[m][r], m_new);
-                    m_run[m][r] = m_new;
-                    l_run[m][r] *= corr[r];
+                    const float m_new = fmaxf(m_run[r], mx[r]);
+                    corr[r] = dtc_weight(m_run[r], m_new);
+                    m_run[r] = m_new;
+                    l_run[r] *= corr[r];
                 }
 #pragma unroll
                 for (int nt = 0; nt < DTC_BN / 8; ++nt) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float p = dtc_weight(s[nt][e], m_run[m][e >> 1]);
+                        const float p = dtc_weight(s[nt][e], m_run[e >> 1]);
                         s[nt][e] = p;
-                        l_run[m][e >> 1] += p;
+                        l_run[e >> 1] += p;
                     }
                 }
 #pragma unroll
                 for (int i = 0; i < DIFF_VDIM / 8; ++i) {
-                    o_acc[m][i][0] *= corr[0];
-                    o_acc[m][i][1] *= corr[0];
-                    o_acc[m][i][2] *= corr[1];
-                    o_acc[m][i][3] *= corr[1];
+                    o_acc[i][0] *= corr[0];
+                    o_acc[i][1] *= corr[0];
+                    o_acc[i][2] *= corr[1];
+                    o_acc[i][3] *= corr[1];
                 }
                 // ---- O_m += P_m V
 #pragma unroll
@@ -235,37 +237,49 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
                         uint32_t b[4];
                         dtc_ldm_t(b, rt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DTC_KP + 2 * DIFF_DIM + dp * 16 +
                                          (lane >> 4) * 8);
-                        dtc_mma(o_acc[m][2 * dp], a, b[0], b[1]);
-                        dtc_mma(o_acc[m][2 * dp + 1], a, b[2], b[3]);
+                        dtc_mma(o_acc[2 * dp], a, b[0], b[1]);
+                        dtc_mma(o_acc[2 * dp + 1], a, b[2], b[3]);
                     }
                 }
             }
         }
         __syncthreads();                                    // the stage is refilled two iterations on
     }
-    if (!has_rows) return;
-
-    // ---- both maps normalised, the difference, the row's root mean square, store
+    // ---- the second map's warps leave their normalised rows (already times lambda) in shared memory, over the ring
+    float* a2 = reinterpret_cast<float*>(Rs);                          // [64][VDIM]; the ring was read out before the barrier
 #pragma unroll
-    for (int m = 0; m < 2; ++m)
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    if (m == 1 && has_rows) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            l_run[m][r] += __shfl_xor_sync(0xffffffffu, l_run[m][r], 1);
-            l_run[m][r] += __shfl_xor_sync(0xffffffffu, l_run[m][r], 2);
+            const float inv2 = lambda / l_run[r];
+            float* dst = a2 + (warp * 16 + g + r * 8) * DIFF_VDIM + 2 * tq;
+#pragma unroll
+            for (int i = 0; i < DIFF_VDIM / 8; ++i)
+                *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o_acc[i][2 * r] * inv2, o_acc[i][2 * r + 1] * inv2);
         }
+    }
+    __syncthreads();
+    if (m == 1 || !has_rows) return;
+
+    // ---- the first map's warps: the difference, the row's root mean square, store
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = warp * 16 + g + r * 8;
-        const float inv1 = 1.0f / l_run[0][r], inv2 = lambda / l_run[1][r];
+        const float inv1 = 1.0f / l_run[r];
+        const float* other = a2 + row * DIFF_VDIM + 2 * tq;
         float ss = 0.0f;
 #pragma unroll
-        for (int i = 0; i < DIFF_VDIM / 8; ++i)
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const float o = o_acc[0][i][2 * r + c] * inv1 - o_acc[1][i][2 * r + c] * inv2;
-                o_acc[0][i][2 * r + c] = o;
-                ss += o * o;
-            }
+        for (int i = 0; i < DIFF_VDIM / 8; ++i) {
+            const float2 x = *reinterpret_cast<const float2*>(other + i * 8);
+            const float o0 = o_acc[i][2 * r] * inv1 - x.x, o1 = o_acc[i][2 * r + 1] * inv1 - x.y;
+            o_acc[i][2 * r] = o0;
+            o_acc[i][2 * r + 1] = o1;
+            ss += o0 * o0 + o1 * o1;
+        }
         ss += __shfl_xor_sync(0xffffffffu, ss, 1);
         ss += __shfl_xor_sync(0xffffffffu, ss, 2);
         if (row >= rows_here) continue;
@@ -273,7 +287,7 @@ __global__ void __launch_bounds__(DTC_THREADS) diff_attention_tc_kernel(
         bf16* dst = out + (long)(tok0 + row) * out_ld + (long)h * DIFF_VDIM + 2 * tq;
 #pragma unroll
         for (int i = 0; i < DIFF_VDIM / 8; ++i) {
-            const __nv_bfloat162 v = __floats2bfloat162_rn(o_acc[0][i][2 * r] * f, o_acc[0][i][2 * r + 1] * f);
+            const __nv_bfloat162 v = __floats2bfloat162_rn(o_acc[i][2 * r] * f, o_acc[i][2 * r + 1] * f);
             *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = v;
         }
     }
