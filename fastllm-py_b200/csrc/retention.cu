@@ -71,9 +71,10 @@ __device__ __forceinline__ void ret_cp(float* dst, const float* src, int bytes) 
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-// PARTS: lanes that share one value column (8 or 16); NI: state elements per lane (dim <= PARTS * NI, a multiple
+// PARTS: lanes that share one value column (8, 16 or 32); NI: state elements per lane (dim <= PARTS * NI, a multiple
 // of 4); COLS: value columns of a block.  A staged token is dim floats of q, dim of k and COLS of v.
-template <int NI, int COLS, int PARTS>
+// FAST: dim == PARTS * NI and every staged row starts 16 bytes aligned, so the inner loop has no bounds to test.
+template <int NI, int COLS, int PARTS, bool FAST>
 __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
     const float* __restrict__ qkv, long ld, float* __restrict__ o, long o_ld, float* __restrict__ state,
     long state_stride, const float* __restrict__ decay, const int* __restrict__ req_start,
@@ -143,39 +144,59 @@ __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
         }
         __syncthreads();
         const float* rows = ret_smem + (long)buf * RET_CHUNK * row_w;
+        const float* mine = rows + 2 * dim + tid / PARTS;   // this column's value of the chunk's first token
+        float* o_at = o + (long)(start + base) * o_ld + (long)h * vdim + col;
 #pragma unroll 4
         for (int c = 0; c < n; ++c) {
             const float* qs = rows + c * row_w;
             const float* ks = qs + dim;
-            const float vj = live ? qs[2 * dim + tid / PARTS] : 0.0f;
+            const float vj = live ? mine[c * row_w] : 0.0f;
             float acc = 0.0f;
+            if (FAST) {
+                const float4* q4 = reinterpret_cast<const float4*>(qs) + part;
+                const float4* k4 = reinterpret_cast<const float4*>(ks) + part;
 #pragma unroll
-            for (int i4 = 0; i4 < NI / 4; ++i4) {
-                const int d0 = i4 * (4 * PARTS) + part * 4;
-                float kk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                if (vec) {                                 // dim is a multiple of 4: four rows are inside or outside together
-                    if (d0 < dim) {
-                        const float4 k4 = *reinterpret_cast<const float4*>(ks + d0);
-                        const float4 q4 = *reinterpret_cast<const float4*>(qs + d0);
-                        kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
-                        qq[0] = q4.x; qq[1] = q4.y; qq[2] = q4.z; qq[3] = q4.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        if (d0 + e < dim) { kk[e] = ks[d0 + e]; qq[e] = qs[d0 + e]; }
+                for (int i4 = 0; i4 < NI / 4; ++i4) {
+                    const float4 kv = k4[i4 * PARTS], qv = q4[i4 * PARTS];
+                    S[i4 * 4 + 0] = g * S[i4 * 4 + 0] + kv.x * vj;
+                    S[i4 * 4 + 1] = g * S[i4 * 4 + 1] + kv.y * vj;
+                    S[i4 * 4 + 2] = g * S[i4 * 4 + 2] + kv.z * vj;
+                    S[i4 * 4 + 3] = g * S[i4 * 4 + 3] + kv.w * vj;
+                    acc += S[i4 * 4 + 0] * qv.x;
+                    acc += S[i4 * 4 + 1] * qv.y;
+                    acc += S[i4 * 4 + 2] * qv.z;
+                    acc += S[i4 * 4 + 3] * qv.w;
                 }
+            } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {              // (rows beyond dim hold zeros and add nothing)
-                    S[i4 * 4 + e] = g * S[i4 * 4 + e] + kk[e] * vj;
-                    acc += S[i4 * 4 + e] * qq[e];
+                for (int i4 = 0; i4 < NI / 4; ++i4) {
+                    const int d0 = i4 * (4 * PARTS) + part * 4;
+                    float kk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (vec) {                             // dim is a multiple of 4: four rows are inside or outside together
+                        if (d0 < dim) {
+                            const float4 k4 = *reinterpret_cast<const float4*>(ks + d0);
+                            const float4 q4 = *reinterpret_cast<const float4*>(qs + d0);
+                            kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
+                            qq[0] = q4.x; qq[1] = q4.y; qq[2] = q4.z; qq[3] = q4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (d0 + e < dim) { kk[e] = ks[d0 + e]; qq[e] = qs[d0 + e]; }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {          // (rows beyond dim hold zeros and add nothing)
+                        S[i4 * 4 + e] = g * S[i4 * 4 + e] + kk[e] * vj;
+                        acc += S[i4 * 4 + e] * qq[e];
+                    }
                 }
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (PARTS == 16) acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            if (part == 0 && live) o[(long)(start + base + c) * o_ld + (long)h * vdim + col] = acc;
+            if (PARTS >= 16) acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+            if (PARTS >= 32) acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+            if (part == 0 && live) o_at[(long)c * o_ld] = acc;
         }
         __syncthreads();                                   // the buffer is staged into again next round
     }
@@ -188,44 +209,66 @@ __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
     }
 }
 
+template <int NI, int COLS, int PARTS, bool FAST>
+static int launch_ret_scan_as(dim3 grid, size_t smem, cudaStream_t stream, const float* qkv, long ld, float* o, long o_ld,
+                              float* state, long state_stride, const float* decay, const int* req_start,
+                              const int* req_ctx, const int* req_qlen, const int* req_slot, int heads, int dim, int vdim,
+                              int vec) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(retention_scan_kernel<NI, COLS, PARTS, FAST>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return fl_launch(retention_scan_kernel<NI, COLS, PARTS, FAST>, grid, dim3(COLS * PARTS), smem, stream, qkv, ld, o,
+                     o_ld, state, state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);
+}
+
 template <int NI, int COLS, int PARTS>
 static int launch_ret_scan(dim3 grid, size_t smem, cudaStream_t stream, const float* qkv, long ld, float* o, long o_ld,
                            float* state, long state_stride, const float* decay, const int* req_start, const int* req_ctx,
                            const int* req_qlen, const int* req_slot, int heads, int dim, int vdim, int vec) {
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(retention_scan_kernel<NI, COLS, PARTS>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    return fl_launch(retention_scan_kernel<NI, COLS, PARTS>, grid, dim3(COLS * PARTS), smem, stream, qkv, ld, o, o_ld,
-                     state, state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);
+    if (vec && dim == NI * PARTS)
+        return launch_ret_scan_as<NI, COLS, PARTS, true>(grid, smem, stream, qkv, ld, o, o_ld, state, state_stride, decay,
+                                                         req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);
+    return launch_ret_scan_as<NI, COLS, PARTS, false>(grid, smem, stream, qkv, ld, o, o_ld, state, state_stride, decay,
+                                                      req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);
 }
 
 // qkv: float [n_tokens, ld] with columns q (heads x dim) | k (heads x dim) | v (heads x vdim), q and k rotated and
 // scaled; o: float [n_tokens, o_ld]; state: [slots, state_stride].  Blocks of 32 columns with eight lanes a column;
-// when those would leave SMs idle (a lone prompt), blocks of 16 columns, with sixteen lanes a column for keys of
-// 64 and more, so that twice the warps share a token's chain.
+// when those would leave SMs idle (a lone prompt), narrower blocks with more lanes a column (16 columns x 16
+// lanes for keys of 64 and more; 8 columns x 32 lanes for keys of 128 and more if SMs would still idle), so that
+// more warps share a token's chain.
 FL_API int fl_retention_scan(const float* qkv, long ld, float* o, long o_ld, float* state, long state_stride,
                              const float* decay, const int* req_start, const int* req_ctx, const int* req_qlen,
                              const int* req_slot, int n_requests, int heads, int dim, int vdim, int num_sms,
                              cudaStream_t stream) {
     if (n_requests <= 0) return 0;
-    const bool narrow = (long)n_requests * heads * ((vdim + 31) / 32) < num_sms && vdim > 16;
-    const bool wide = narrow && dim >= 64;                   // sixteen lanes a column
-    const int cols = narrow ? 16 : 32;
+    if (dim < 1 || dim > 256 || heads > 65535) return (int)cudaErrorInvalidValue;
+    const long units = (long)n_requests * heads;
+    int cols = 32, parts = 8;
+    if (units * ((vdim + 31) / 32) < num_sms && vdim > 16) {
+        cols = 16;
+        if (dim >= 64) parts = 16;
+        if (dim >= 128 && units * ((vdim + 15) / 16) < 2 * num_sms && vdim > 8) { cols = 8; parts = 32; }
+    }
     const int col_blocks = (vdim + cols - 1) / cols;
-    if (dim < 1 || dim > 256 || heads > 65535 || col_blocks > 65535) return (int)cudaErrorInvalidValue;
+    if (col_blocks > 65535) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)2 * RET_CHUNK * (2 * dim + cols) * sizeof(float);
     const int vec = dim % 4 == 0 && vdim % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qkv % 16) == 0;
     dim3 grid(n_requests, heads, col_blocks);
 #define FL_RET_ARGS grid, smem, stream, qkv, ld, o, o_ld, state, state_stride, decay, req_start, req_ctx, req_qlen, \
                     req_slot, heads, dim, vdim, vec
-    if (wide) {
+    if (parts == 32) {
+        if (dim <= 128) return launch_ret_scan<4, 8, 32>(FL_RET_ARGS);
+        return launch_ret_scan<8, 8, 32>(FL_RET_ARGS);
+    }
+    if (parts == 16) {
         if (dim <= 64) return launch_ret_scan<4, 16, 16>(FL_RET_ARGS);
         if (dim <= 128) return launch_ret_scan<8, 16, 16>(FL_RET_ARGS);
         return launch_ret_scan<16, 16, 16>(FL_RET_ARGS);
     }
-    if (narrow) {
+    if (cols == 16) {
         if (dim <= 32) return launch_ret_scan<4, 16, 8>(FL_RET_ARGS);
         return launch_ret_scan<8, 16, 8>(FL_RET_ARGS);
     }

@@ -354,8 +354,9 @@ def test_clamped_unit_and_pair_norm_kernels(dtype):
     assert float((few.double() - (normed * w1.double())[rows.cpu().long()]).abs().max()) <= 4 * tol
 
 
-@pytest.mark.parametrize("dim,vdim,window", [(32, 64, 70), (16, 16, None), (64, 128, 33), (48, 80, 81)])
-def test_tensor_core_attention_equals_the_cuda_core_one(dim, vdim, window):
+@pytest.mark.parametrize("dim,vdim,window,heads,kv_heads", [(32, 64, 70, 4, 2), (16, 16, None, 6, 2), (64, 128, 33, 3, 3),
+                                                           (48, 80, 81, 8, 1), (128, 128, 90, 2, 1)])
+def test_tensor_core_attention_equals_the_cuda_core_one(dim, vdim, window, heads, kv_heads):
     """Scattered pages, a prompt portion behind cached tokens beside single tokens, a standout key just
     inside the window of one query and just outside that of the next."""
     from types import SimpleNamespace
@@ -363,7 +364,7 @@ def test_tensor_core_attention_equals_the_cuda_core_one(dim, vdim, window):
     from fastllm_py_b200.native import ops
 
     gen = torch.Generator().manual_seed(dim + vdim)
-    heads, kv_heads, page = 4, 2, 16
+    page = 16
     ctx_lens, q_lens = [37, 150, 0, 201], [100, 1, 70, 1]
     row_w = 2 * dim + vdim
     n_pages = sum(-(-(c + q) // page) for c, q in zip(ctx_lens, q_lens))
