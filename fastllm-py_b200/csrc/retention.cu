@@ -71,15 +71,26 @@ __device__ __forceinline__ void ret_cp(float* dst, const float* src, int bytes) 
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
+// One state element's step: S <- g S + k v, then the read-out's sum takes S q.  Written with explicit roundings so
+// that every path through the kernel (four tokens at a time, a portion's last tokens one by one) does the same
+// arithmetic: a token's result does not depend on where a portion was cut.
+__device__ __forceinline__ void ret_update(float& S, float& acc, float g, float k, float q, float v) {
+    S = __fmaf_rn(g, S, __fmul_rn(k, v));
+    acc = __fmaf_rn(S, q, acc);
+}
+
 // PARTS: lanes that share one value column (8, 16 or 32); NI: state elements per lane (dim <= PARTS * NI, a multiple
-// of 4); COLS: value columns of a block.  A staged token is dim floats of q, dim of k and COLS of v.
-// FAST: dim == PARTS * NI and every staged row starts 16 bytes aligned, so the inner loop has no bounds to test.
-template <int NI, int COLS, int PARTS, bool FAST>
+// of 4); COLS: value columns of a block.  A staged token is dim floats of q, dim of k and COLS of v; with VEC
+// every staged piece starts 16 bytes aligned (dim and vdim multiples of 4) and rows are read four floats at a time;
+// FULL: dim == PARTS * NI, so no lane's rows lie beyond dim and the loads have no bounds to test.
+// Lane `part` holds, of its column, rows (i / 4) * 4 PARTS + part * 4 + i % 4: four neighbours at a time, so that
+// the lanes of a column read consecutive bytes of a staged q or k row with one 16-byte load each.
+template <int NI, int COLS, int PARTS, bool VEC, bool FULL>
 __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
     const float* __restrict__ qkv, long ld, float* __restrict__ o, long o_ld, float* __restrict__ state,
     long state_stride, const float* __restrict__ decay, const int* __restrict__ req_start,
     const int* __restrict__ req_ctx, const int* __restrict__ req_qlen, const int* __restrict__ req_slot, int heads,
-    int dim, int vdim, int vec) {
+    int dim, int vdim) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ __align__(16) float ret_smem[];      // two buffers of [CHUNK][2 dim + COLS]
@@ -89,8 +100,6 @@ __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
     const int start = req_start[r], qlen = req_qlen[r];
     const bool live = col < vdim;
     float* srow = state + (long)req_slot[r] * state_stride + ((long)h * vdim + (live ? col : 0)) * dim;
-    // lane `part` holds, of its column, rows (i / 4) * 4 PARTS + part * 4 + i % 4: four neighbours at a time, so that
-    // the lanes of a column read consecutive bytes of a staged q or k row with one 16-byte load each
     float S[NI];
     const bool fresh = req_ctx[r] == 0;
 #pragma unroll
@@ -103,11 +112,11 @@ __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
     const long v_off = (long)2 * heads * dim + (long)h * vdim + col0;
     const int v_cols = min(COLS, vdim - col0);
 
-    // stage chunk `base` into buffer `buf`: pieces of 4 floats where every start is 16-byte aligned, else float by float
+    // stage chunk `base` into buffer `buf`
     auto stage = [&](int base, int buf) {
         float* dst = ret_smem + (long)buf * RET_CHUNK * row_w;
         const int n = min(RET_CHUNK, qlen - base);
-        if (vec) {
+        if (VEC) {
             const int per = row_w / 4, qk4 = dim / 4;
             for (int i = tid; i < n * per; i += blockDim.x) {
                 const int c = i / per, e = i - c * per;
@@ -131,6 +140,20 @@ __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    // the four (or fewer) state rows of group i4 that token row `rowp` (q at 0, k at dim) holds for this lane
+    auto fetch = [&](const float* rowp, int i4, float* out4) {
+        const int d0 = i4 * (4 * PARTS) + part * 4;
+        if (VEC && FULL) {
+            const float4 v = reinterpret_cast<const float4*>(rowp)[i4 * PARTS + part];
+            out4[0] = v.x; out4[1] = v.y; out4[2] = v.z; out4[3] = v.w;
+        } else if (VEC) {
+            const float4 v = d0 < dim ? *reinterpret_cast<const float4*>(rowp + d0) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            out4[0] = v.x; out4[1] = v.y; out4[2] = v.z; out4[3] = v.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) out4[e] = d0 + e < dim ? rowp[d0 + e] : 0.0f;     // (rows beyond dim add nothing)
+        }
+    };
 
     stage(0, 0);
     int buf = 0;
@@ -146,57 +169,56 @@ __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
         const float* rows = ret_smem + (long)buf * RET_CHUNK * row_w;
         const float* mine = rows + 2 * dim + tid / PARTS;   // this column's value of the chunk's first token
         float* o_at = o + (long)(start + base) * o_ld + (long)h * vdim + col;
-#pragma unroll 4
-        for (int c = 0; c < n; ++c) {
-            const float* qs = rows + c * row_w;
-            const float* ks = qs + dim;
-            const float vj = live ? mine[c * row_w] : 0.0f;
-            float acc = 0.0f;
-            if (FAST) {
-                const float4* q4 = reinterpret_cast<const float4*>(qs) + part;
-                const float4* k4 = reinterpret_cast<const float4*>(ks) + part;
+        // Four tokens at a time, written out so that only the state's own chain (one multiply-add a token) stands
+        // between them: the tokens' read-out sums and their reductions over the lanes run side by side.  A
+        // portion's last one to three tokens go one by one, with the same arithmetic.
+        for (int c0 = 0; c0 < n; c0 += 4) {
+            const int m = min(4, n - c0);
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, vj[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) vj[u] = (live && u < m) ? mine[(c0 + u) * row_w] : 0.0f;
+            if (m == 4) {
 #pragma unroll
                 for (int i4 = 0; i4 < NI / 4; ++i4) {
-                    const float4 kv = k4[i4 * PARTS], qv = q4[i4 * PARTS];
-                    S[i4 * 4 + 0] = g * S[i4 * 4 + 0] + kv.x * vj;
-                    S[i4 * 4 + 1] = g * S[i4 * 4 + 1] + kv.y * vj;
-                    S[i4 * 4 + 2] = g * S[i4 * 4 + 2] + kv.z * vj;
-                    S[i4 * 4 + 3] = g * S[i4 * 4 + 3] + kv.w * vj;
-                    acc += S[i4 * 4 + 0] * qv.x;
-                    acc += S[i4 * 4 + 1] * qv.y;
-                    acc += S[i4 * 4 + 2] * qv.z;
-                    acc += S[i4 * 4 + 3] * qv.w;
+                    float kv[4][4], qv[4][4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float* rowp = rows + (c0 + u) * row_w;
+                        fetch(rowp, i4, qv[u]);
+                        fetch(rowp + dim, i4, kv[u]);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) ret_update(S[i4 * 4 + e], acc[u], g, kv[u][e], qv[u][e], vj[u]);
                 }
             } else {
+                for (int u = 0; u < m; ++u) {
+                    const float* rowp = rows + (c0 + u) * row_w;
+                    const float vu = live ? mine[(c0 + u) * row_w] : 0.0f;
+                    float a = 0.0f;
 #pragma unroll
-                for (int i4 = 0; i4 < NI / 4; ++i4) {
-                    const int d0 = i4 * (4 * PARTS) + part * 4;
-                    float kk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    if (vec) {                             // dim is a multiple of 4: four rows are inside or outside together
-                        if (d0 < dim) {
-                            const float4 k4 = *reinterpret_cast<const float4*>(ks + d0);
-                            const float4 q4 = *reinterpret_cast<const float4*>(qs + d0);
-                            kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
-                            qq[0] = q4.x; qq[1] = q4.y; qq[2] = q4.z; qq[3] = q4.w;
-                        }
-                    } else {
+                    for (int i4 = 0; i4 < NI / 4; ++i4) {
+                        float kk[4], qq[4];
+                        fetch(rowp, i4, qq);
+                        fetch(rowp + dim, i4, kk);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (d0 + e < dim) { kk[e] = ks[d0 + e]; qq[e] = qs[d0 + e]; }
+                        for (int e = 0; e < 4; ++e) ret_update(S[i4 * 4 + e], a, g, kk[e], qq[e], vu);
                     }
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {          // (rows beyond dim hold zeros and add nothing)
-                        S[i4 * 4 + e] = g * S[i4 * 4 + e] + kk[e] * vj;
-                        acc += S[i4 * 4 + e] * qq[e];
-                    }
+                    if (u == 0) acc[0] = a;
+                    else if (u == 1) acc[1] = a;
+                    else acc[2] = a;
                 }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (PARTS >= 16) acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            if (PARTS >= 32) acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (part == 0 && live) o_at[(long)c * o_ld] = acc;
+#pragma unroll
+            for (int o_ = 1; o_ < PARTS; o_ <<= 1)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o_);
+            if (part == 0 && live) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (u < m) o_at[(long)(c0 + u) * o_ld] = acc[u];
+            }
         }
         __syncthreads();                                   // the buffer is staged into again next round
     }
@@ -209,18 +231,17 @@ __global__ void __launch_bounds__(COLS * PARTS) retention_scan_kernel(
     }
 }
 
-template <int NI, int COLS, int PARTS, bool FAST>
+template <int NI, int COLS, int PARTS, bool VEC, bool FULL>
 static int launch_ret_scan_as(dim3 grid, size_t smem, cudaStream_t stream, const float* qkv, long ld, float* o, long o_ld,
                               float* state, long state_stride, const float* decay, const int* req_start,
-                              const int* req_ctx, const int* req_qlen, const int* req_slot, int heads, int dim, int vdim,
-                              int vec) {
+                              const int* req_ctx, const int* req_qlen, const int* req_slot, int heads, int dim, int vdim) {
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(retention_scan_kernel<NI, COLS, PARTS, FAST>,
+        cudaError_t e = cudaFuncSetAttribute(retention_scan_kernel<NI, COLS, PARTS, VEC, FULL>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return fl_launch(retention_scan_kernel<NI, COLS, PARTS, FAST>, grid, dim3(COLS * PARTS), smem, stream, qkv, ld, o,
-                     o_ld, state, state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);
+    return fl_launch(retention_scan_kernel<NI, COLS, PARTS, VEC, FULL>, grid, dim3(COLS * PARTS), smem, stream, qkv, ld, o,
+                     o_ld, state, state_stride, decay, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim);
 }
 
 template <int NI, int COLS, int PARTS>
@@ -228,29 +249,35 @@ static int launch_ret_scan(dim3 grid, size_t smem, cudaStream_t stream, const fl
                            float* state, long state_stride, const float* decay, const int* req_start, const int* req_ctx,
                            const int* req_qlen, const int* req_slot, int heads, int dim, int vdim, int vec) {
     if (vec && dim == NI * PARTS)
-        return launch_ret_scan_as<NI, COLS, PARTS, true>(grid, smem, stream, qkv, ld, o, o_ld, state, state_stride, decay,
-                                                         req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);
-    return launch_ret_scan_as<NI, COLS, PARTS, false>(grid, smem, stream, qkv, ld, o, o_ld, state, state_stride, decay,
-                                                      req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, vec);
+        return launch_ret_scan_as<NI, COLS, PARTS, true, true>(grid, smem, stream, qkv, ld, o, o_ld, state, state_stride,
+                                                               decay, req_start, req_ctx, req_qlen, req_slot, heads, dim,
+                                                               vdim);
+    if (vec)
+        return launch_ret_scan_as<NI, COLS, PARTS, true, false>(grid, smem, stream, qkv, ld, o, o_ld, state, state_stride,
+                                                                decay, req_start, req_ctx, req_qlen, req_slot, heads, dim,
+                                                                vdim);
+    return launch_ret_scan_as<NI, COLS, PARTS, false, false>(grid, smem, stream, qkv, ld, o, o_ld, state, state_stride, decay,
+                                                      req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim);
 }
 
 // qkv: float [n_tokens, ld] with columns q (heads x dim) | k (heads x dim) | v (heads x vdim), q and k rotated and
 // scaled; o: float [n_tokens, o_ld]; state: [slots, state_stride].  Blocks of 32 columns with eight lanes a column;
 // when those would leave SMs idle (a lone prompt), narrower blocks with more lanes a column (16 columns x 16
 // lanes for keys of 64 and more; 8 columns x 32 lanes for keys of 128 and more if SMs would still idle), so that
-// more warps share a token's chain.
+// more warps share a token's chain.  The lanes of a column fix the order of the read-out's sum: with `fixed_order`
+// there are always eight, so that a token's result never depends on what else is in the step.
 FL_API int fl_retention_scan(const float* qkv, long ld, float* o, long o_ld, float* state, long state_stride,
                              const float* decay, const int* req_start, const int* req_ctx, const int* req_qlen,
                              const int* req_slot, int n_requests, int heads, int dim, int vdim, int num_sms,
-                             cudaStream_t stream) {
+                             int fixed_order, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (dim < 1 || dim > 256 || heads > 65535) return (int)cudaErrorInvalidValue;
     const long units = (long)n_requests * heads;
     int cols = 32, parts = 8;
     if (units * ((vdim + 31) / 32) < num_sms && vdim > 16) {
         cols = 16;
-        if (dim >= 64) parts = 16;
-        if (dim >= 128 && units * ((vdim + 15) / 16) < 2 * num_sms && vdim > 8) { cols = 8; parts = 32; }
+        if (dim >= 64 && !fixed_order) parts = 16;
+        if (dim >= 128 && !fixed_order && units * ((vdim + 15) / 16) < 2 * num_sms && vdim > 8) { cols = 8; parts = 32; }
     }
     const int col_blocks = (vdim + cols - 1) / cols;
     if (col_blocks > 65535) return (int)cudaErrorInvalidValue;
@@ -270,7 +297,9 @@ FL_API int fl_retention_scan(const float* qkv, long ld, float* o, long o_ld, flo
     }
     if (cols == 16) {
         if (dim <= 32) return launch_ret_scan<4, 16, 8>(FL_RET_ARGS);
-        return launch_ret_scan<8, 16, 8>(FL_RET_ARGS);
+        if (dim <= 64) return launch_ret_scan<8, 16, 8>(FL_RET_ARGS);
+        if (dim <= 128) return launch_ret_scan<16, 16, 8>(FL_RET_ARGS);
+        return launch_ret_scan<32, 16, 8>(FL_RET_ARGS);
     }
     if (dim <= 32) return launch_ret_scan<4, 32, 8>(FL_RET_ARGS);
     if (dim <= 64) return launch_ret_scan<8, 32, 8>(FL_RET_ARGS);

@@ -413,10 +413,11 @@ def retention_prep(proj, work, heads, dim, vdim, rot, cos, sin, positions, k_sca
 _sm_counts: dict = {}
 
 
-def retention_scan(work, o, state, decay, step, heads, dim, vdim):
+def retention_scan(work, o, state, decay, step, heads, dim, vdim, fixed_order=False):
     """Per request and head S <- decay S + k v^T, o = S^T q over the step's tokens; q | k | v are the float32 columns
     of `work`, `o` float32 [N, heads * vdim]; state rows [heads, vdim, dim] float32 are read (unless the request
-    starts) and written."""
+    starts) and written.  `fixed_order`: the read-out's sum keeps one order whatever the step's shape (otherwise a
+    lone prompt spreads a column over more lanes than a batch does)."""
     _require_cuda(work, o, state, decay)
     if work.dtype != torch.float32 or o.dtype != torch.float32 or state.dtype != torch.float32 or \
             decay.dtype != torch.float32:
@@ -426,10 +427,10 @@ def retention_scan(work, o, state, decay, step, heads, dim, vdim):
         sms = _sm_counts[work.device] = torch.cuda.get_device_properties(work.device).multi_processor_count
     fn = _fn("retention", "fl_retention_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p,
                                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                c_void_p])
+                                                c_int, c_void_p])
     _check(fn(_ptr(work), _ld(work), _ptr(o), _ld(o), _ptr(state), state.stride(0), _ptr(decay), _ptr(step.req_start),
               _ptr(step.req_ctx), _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, dim, vdim, sms,
-              _stream()), "retention_scan")
+              int(fixed_order), _stream()), "retention_scan")
 
 
 def retention_gated_norm(o, proj, gate_col, out, heads, vdim, eps):

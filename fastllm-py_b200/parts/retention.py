@@ -90,7 +90,8 @@ class Retention(Part):
         work = ws.rows("retention_qkv", n, self.qk_cols + self.hv, torch.float32)
         ops.retention_prep(proj, work, self.heads, self.dim, self.vdim, rot, cos, sin, step.positions, self.k_scale)
         o = ws.rows("retention_o", n, self.hv, torch.float32)
-        ops.retention_scan(work, o, cache.tensor, self.decay, step, self.heads, self.dim, self.vdim)
+        ops.retention_scan(work, o, cache.tensor, self.decay, step, self.heads, self.dim, self.vdim,
+                           fixed_order=dt == torch.float32)     # the 32-bit path: cuts and batches agree bit for bit
         y = ws.rows("retention_y", n, self.hv, dt)
         ops.retention_gated_norm(o, proj, self.qk_cols + self.hv, y, self.heads, self.vdim, self.norm_eps)
         return self.o.forward(y, out, defer=True)

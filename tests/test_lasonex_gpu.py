@@ -446,3 +446,45 @@ def test_clamped_unit_in_the_tensor_core_products_epilogue():
         assert float((g == limit).float().mean()) > 0.05                  # the limit is reached often
         assert float((out.float() - ref).abs().max()) <= 0.03 * float(ref.abs().max()) + 1e-2, m
     assert taken >= 1
+
+
+@pytest.mark.parametrize("dim,vdim", [(128, 32), (64, 24), (96, 40), (256, 16), (20, 12)])
+def test_retention_scan_shapes_agree_with_a_plain_loop(dim, vdim):
+    """A lone prompt spreads a value column over 16 or 32 lanes, a batch (and the 32-bit path, always) over 8:
+    all against a float64 loop, a portion continuing from a saved state included."""
+    from types import SimpleNamespace
+
+    from fastllm_py_b200.native import ops
+
+    gen = torch.Generator().manual_seed(dim)
+    heads, n = 2, 75
+    work = (torch.randn(n, 2 * heads * dim + heads * vdim, generator=gen) * 0.5).cuda()
+    decay = torch.tensor([0.9, 0.999]).cuda()
+    q, k, v = (t.double().cpu() for t in (work[:, :heads * dim], work[:, heads * dim:2 * heads * dim], work[:, 2 * heads * dim:]))
+    S = torch.zeros(heads, dim, vdim, dtype=torch.float64)
+    want = torch.zeros(n, heads * vdim, dtype=torch.float64)
+    for t in range(n):
+        for h in range(heads):
+            S[h] = float(decay[h]) * S[h] + torch.outer(k[t, h * dim:(h + 1) * dim], v[t, h * vdim:(h + 1) * vdim])
+            want[t, h * vdim:(h + 1) * vdim] = S[h].T @ q[t, h * dim:(h + 1) * dim]
+
+    def run(cuts, fixed):
+        state = torch.full((3, heads * vdim * dim), 7.0, device="cuda")           # what an earlier request left
+        out = torch.zeros(n, heads * vdim, device="cuda")
+        at = 0
+        for length in cuts:
+            step = SimpleNamespace(req_start=torch.tensor([0, length], dtype=torch.int32).cuda(),
+                                   req_ctx=torch.tensor([at], dtype=torch.int32).cuda(),
+                                   req_qlen=torch.tensor([length], dtype=torch.int32).cuda(),
+                                   req_slot=torch.tensor([1], dtype=torch.int32).cuda(), n_requests=1)
+            ops.retention_scan(work[at:at + length], out[at:at + length], state, decay, step, heads, dim, vdim, fixed)
+            at += length
+        return out.cpu().double(), state[1].cpu().double()
+
+    scale = float(want.abs().max())
+    whole, s_whole = run([n], False)
+    fixed, s_fixed = run([n], True)
+    cut, s_cut = run([33, 1, 2, 39], True)
+    assert float((whole - want).abs().max()) <= 1e-5 * scale and float((fixed - want).abs().max()) <= 1e-5 * scale
+    assert torch.equal(cut, fixed) and torch.equal(s_cut, s_fixed)                 # one order whatever the cut
+    assert float((s_whole.view(heads, vdim, dim) - S.transpose(1, 2)).abs().max()) <= 1e-5 * float(S.abs().max())
