@@ -677,10 +677,10 @@ def lasonex_config(size):
 
     z = LASONEX_SIZES[size]
     a, r = z["attention"], z["retention"]
-    attention = DifferentialAttentionConfig(a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["dim"] ** -0.5, 0.5,
-                                            a["window"], RotationConfig(50000.0, a["dim"], ("yarn", 8.0, 2048.0, 32.0, 1.0)))
+    attention = DifferentialAttentionConfig(a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["dim"] ** -0.5, 0.8,
+                                            a["window"], RotationConfig(10000.0, a["dim"], ("yarn", 4.0, 4096.0, 32.0, 1.0)))
     decay = tuple(1.0 - 2.0 ** (-5.0 - 6.0 * h / max(1, r["heads"] - 1)) for h in range(r["heads"]))
-    retention = RetentionConfig(r["heads"], r["dim"], r["vdim"], decay, RotationConfig(1e6, r["dim"], None))
+    retention = RetentionConfig(r["heads"], r["dim"], r["vdim"], decay, RotationConfig(10000.0, r["dim"], None))
     dense = ClampedFeedForwardConfig(z["dense_ff"], 7.0)
     routed = GroupedExpertsConfig(z["experts"], z["top"], z["groups"][0], z["groups"][1], z["expert_ff"], 7.0)
     layers = []
@@ -692,7 +692,8 @@ def lasonex_config(size):
             layers.append(LasonexLayerConfig("retention", retention, routed))
         else:
             layers.append(LasonexLayerConfig("attention", attention, routed))
-    return LasonexConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, embedding_scale=12.0, layers=tuple(layers))
+    return LasonexConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, embedding_scale=float(z["width"]) ** 0.5,
+                         layers=tuple(layers))
 
 
 def lasonex_decode_bytes(cfg, batch, context):

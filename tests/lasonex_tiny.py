@@ -37,11 +37,11 @@ def retention(heads=2, dim=16, vdim=8, decay=None, rot=8, base=10000.0):
                                            "rot": {"base": base, "dims": rot}, "vdim": vdim}}
 
 
-def dense(ff=48, limit=1.0):
+def dense(ff=48, limit=0.75):
     return {"ff": ff, "kind": "dense", "limit": limit}
 
 
-def moe(experts=6, top=2, ff=24, limit=1.5, groups=None):
+def moe(experts=6, top=2, ff=24, limit=1.25, groups=None):
     router = {"experts": experts, "top": top}
     if groups is not None:
         router["groups"] = {"count": groups[0], "keep": groups[1]}

@@ -18,7 +18,7 @@ from fastllm_py_b200.weights import write_model_folder
 
 YARN = (4.0, 64, 8.0, 1.0)
 RAW = lt.config([(lt.attention(4, 2, 16, 24, window=11, rot=8, scaling=YARN), lt.dense(48, 0.8)),
-                 (lt.retention(3, 12, 20, rot=6), lt.moe(6, 2, 24, 1.5, groups=(3, 2))),
+                 (lt.retention(3, 12, 20, rot=6), lt.moe(6, 2, 24, 1.25, groups=(3, 2))),
                  (lt.attention(3, 3, 10, 6, window=None, rot=10, diff=0.7), None),
                  (lt.retention(1, 8, 8, rot=0), lt.moe(4, 4, 8, 2.0))], vocab=97, width=40, embed_scale=5.0)
 
@@ -89,7 +89,7 @@ def test_a_written_folder_loads_by_its_architecture_string(tmp_path):
         assert {k: tuple(f.get_slice(k).get_shape()) for k in f.keys()} == lt.tensor_shapes(RAW)
 
 
-@pytest.mark.parametrize("scaling", [None, ("yarn",) + YARN, ("yarn", 8.0, 2048, 32.0, 1.0)])
+@pytest.mark.parametrize("scaling", [None, ("yarn",) + YARN, ("yarn", 6.0, 1024, 16.0, 2.0)])
 def test_rotary_tables_follow_the_blend(scaling):
     """The position part's tables against the oracle's own (written apart from it)."""
     spec = PartSpec("rotary", dict(rot_dim=12, theta=700.0, scaling=scaling, exact=True))

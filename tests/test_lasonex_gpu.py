@@ -26,8 +26,8 @@ YARN = (4.0, 64, 8.0, 1.0)
 # without feed-forward, a model of one mixer kind only
 MODELS = {
     "mix": dict(layers=[(lt.attention(4, 2, 16, 24, window=11, rot=8, scaling=YARN), lt.dense(48, 0.8)),
-                        (lt.retention(2, 16, 8, rot=8), lt.moe(6, 2, 24, 1.5, groups=(3, 2))),
-                        (lt.attention(4, 2, 16, 24, window=30, rot=16), lt.moe(6, 2, 24, 1.5, groups=(3, 2))),
+                        (lt.retention(2, 16, 8, rot=8), lt.moe(6, 2, 24, 1.25, groups=(3, 2))),
+                        (lt.attention(4, 2, 16, 24, window=30, rot=16), lt.moe(6, 2, 24, 1.25, groups=(3, 2))),
                         (lt.retention(2, 16, 8, rot=8), None)], vocab=97, width=40, eps=1e-5, scale=3.0, page=8),
     "odd": dict(layers=[(lt.attention(3, 3, 10, 7, window=7, rot=6, base=500.0, diff=0.7), lt.moe(5, 1, 10, 0.5)),
                         (lt.retention(3, 13, 35, rot=12, decay=[0.5, 0.93, 0.999]), lt.dense(30, 2.5)),
@@ -37,9 +37,9 @@ MODELS = {
                 vocab=61, width=36, eps=1e-6, scale=1.0, page=16),
     # sizes that the tensor-core kernels take in bfloat16 (multiples of 16 and 32 throughout, the grouped expert
     # products from 64 prompt tokens on)
-    "even": dict(layers=[(lt.attention(4, 2, 32, 64, window=40, rot=32, scaling=(8.0, 128, 16.0, 1.0)), lt.moe(8, 2, 64, 1.5, groups=(4, 2))),
-                         (lt.retention(4, 32, 32, rot=16), lt.dense(128, 1.0)),
-                         (lt.attention(8, 2, 16, 32, window=70, rot=8), lt.moe(8, 2, 64, 1.5))],
+    "even": dict(layers=[(lt.attention(4, 2, 32, 64, window=44, rot=32, scaling=(8.0, 128, 16.0, 1.0)), lt.moe(8, 2, 64, 1.25, groups=(4, 2))),
+                         (lt.retention(4, 32, 48, rot=16), lt.dense(128, 0.9)),
+                         (lt.attention(8, 2, 16, 32, window=70, rot=8), lt.moe(8, 2, 64, 2.0))],
                  vocab=80, width=64, eps=1e-6, scale=8.0, page=16),
 }
 LENGTHS = {"mix": [1, 2, 9, 23, 40, 77], "odd": [3, 30, 64, 51], "even": [150, 70, 90]}
@@ -306,7 +306,7 @@ def test_router_choice_with_groups_follows_the_oracle():
     from fastllm_py_b200.native import ops
 
     gen = torch.Generator().manual_seed(3)
-    for experts, top, groups in ((12, 3, (4, 2)), (16, 4, (4, 3)), (6, 2, (6, 2)), (6, 1, (6, 1)), (8, 8, (2, 2)), (9, 2, None), (40, 5, (5, 2))):
+    for experts, top, groups in ((12, 3, (4, 2)), (20, 4, (5, 3)), (6, 2, (6, 2)), (6, 1, (6, 1)), (8, 8, (2, 2)), (9, 2, None), (40, 5, (5, 2))):
         z = torch.randn(70, experts, generator=gen) * 2.0
         r = {"experts": experts, "top": top}
         if groups:
