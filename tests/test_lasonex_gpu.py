@@ -488,3 +488,101 @@ def test_retention_scan_shapes_agree_with_a_plain_loop(dim, vdim):
     assert float((whole - want).abs().max()) <= 1e-5 * scale and float((fixed - want).abs().max()) <= 1e-5 * scale
     assert torch.equal(cut, fixed) and torch.equal(s_cut, s_fixed)                 # one order whatever the cut
     assert float((s_whole.view(heads, vdim, dim) - S.transpose(1, 2)).abs().max()) <= 1e-5 * float(S.abs().max())
+
+
+def test_parallel_block_under_a_norm_of_another_kind(tmp_path):
+    """Another design uses the parallel block, the retention mixer and the clamped unit with a norm part of its own that
+    knows nothing of a second pending tensor (and a second layer without feed-forward): the residual stream adds both
+    sums before it hands the row to that norm."""
+    import json
+    from dataclasses import dataclass
+
+    from fastllm_py_b200 import Model, StepEntry
+    from fastllm_py_b200.config import register_architecture
+    from fastllm_py_b200.parts import LayerRun, LayerSpec, ModelPlan, Part, PartSpec, register_part
+
+    @register_part("norm", "toy_rms_plus_one")
+    class RmsPlusOne(Part):
+        category = "norm"
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.size, self.eps = int(spec.params["size"]), float(spec.params["eps"])
+
+        def weight_shapes(self):
+            return {"weight": (self.size,)}
+
+        def load(self, tensors):
+            self.weight = tensors["weight"].float()
+
+        def apply(self, stream, out, rows=None):
+            assert getattr(stream, "extra", None) is None
+            x = stream.x
+            if stream.pending is not None and rows is None:
+                x += stream.pending.float()
+                stream.pending = None
+            elif stream.pending is not None:
+                x = x[rows.long()] + stream.pending[rows.long()].float()
+            elif rows is not None:
+                x = x[rows.long()]
+            out.copy_((x * torch.rsqrt(x.pow(2).mean(dim=1, keepdim=True) + self.eps) * (1.0 + self.weight)).to(out.dtype))
+
+    @dataclass(frozen=True)
+    class Toy4Config:
+        vocab: int
+        width: int
+
+        @classmethod
+        def from_hf(cls, raw):
+            return cls(raw["vocab"], raw["width"])
+
+        def to_hf(self):
+            return {"architectures": ["Toy4ForCausalLM"], "vocab": self.vocab, "width": self.width}
+
+    decay, limit = (0.9, 0.99), 0.8
+
+    def make_plan(cfg, names=None):
+        w = cfg.width
+
+        def norm(n):
+            return PartSpec("toy_rms_plus_one", dict(size=w, eps=1e-5), {"weight": n})
+
+        def mixer(i):
+            return PartSpec("retention", dict(hidden_size=w, heads=2, dim=8, vdim=12, decay=decay, norm_eps=1e-5,
+                                              position=PartSpec("rotary", dict(rot_dim=4, theta=100.0, scaling=None, exact=True))),
+                            {s: f"l{i}.mix.{s}" for s in ("q", "k", "v", "g", "o")})
+
+        ff = PartSpec("glu", dict(hidden_size=w, intermediate_size=20, activation="clamped_swish", activation_params=(limit, 1.702)),
+                      {s: f"l0.mlp.{s}" for s in ("gate", "up", "down")})
+        layers = [LayerSpec("parallel", mixer(0), ff, {"mixer": norm("l0.norm1"), "feed_forward": norm("l0.norm2")}),
+                  LayerSpec("parallel", mixer(1), None, {"mixer": norm("l1.norm1")})]
+        io = dict(vocab_size=cfg.vocab, hidden_size=w)
+        return ModelPlan(w, cfg.vocab, 256, PartSpec("table", io, {"weight": "embed"}), layers, [LayerRun(0), LayerRun(1)],
+                         norm("final.norm"), PartSpec("linear", io, {"weight": "head"}))
+
+    register_architecture("Toy4ForCausalLM", Toy4Config, make_plan)
+    raw = lt.config([(lt.retention(2, 8, 12, rot=4, base=100.0, decay=decay), lt.dense(20, limit)),
+                     (lt.retention(2, 8, 12, rot=4, base=100.0, decay=decay), None)], vocab=30, width=24, eps=1e-5)
+    w = lt.weights(raw, seed=21)
+    folder = tmp_path / "toy4"
+    lt.write(raw, w, folder)
+    (folder / "config.json").write_text(json.dumps(Toy4Config(30, 24).to_hf()))
+    toks = np.random.default_rng(3).integers(0, 30, size=31).tolist()
+
+    def norm(x, weight):
+        return plain.rms(x, 1e-5) * (1.0 + weight.double())
+
+    x = w["embed"].double()[toks]
+    for i in range(2):
+        mix = {s: w[f"l{i}.mix.{s}"].double() for s in ("q", "k", "v", "g", "o")}
+        y, _ = plain.retention(norm(x, w[f"l{i}.norm1"]), mix, raw["layers"][i]["mixer"], 1e-5)
+        if i == 0:
+            y = y + plain.clamped_unit(norm(x, w["l0.norm2"]), *(w[f"l0.mlp.{s}"].double() for s in ("gate", "up", "down")), limit)
+        x = x + y
+    want = (norm(x, w["final.norm"]) @ w["head"].double().T).float()
+    eng = Model.load(folder, dtype="float32", page_size=8, max_tokens=64, max_requests=2, max_batched_tokens=64,
+                     max_model_len=64, cuda_graph=False).engine
+    eng.begin("a")
+    got = torch.cat([eng.step([StepEntry("a", toks[:17], list(range(17)))]).cpu().clone(),
+                     eng.step([StepEntry("a", toks[17:], [0, 5, 13])]).cpu().clone()])
+    assert float((got - want[list(range(17)) + [17, 22, 30]]).abs().max()) <= 2e-4 * max(1.0, float(want.abs().max()))
