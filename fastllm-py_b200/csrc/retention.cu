@@ -7,15 +7,18 @@
 // silu(gate).
 //
 //   retention_prep        per token: rotation and scale of every head into a float work row q | k | v
-//   retention_scan        per (request, head, 32 or 16 value columns): the recurrence over the portion's tokens,
-//                         one value column's state spread over eight lanes' registers, the tokens' q, k and
-//                         v staged through shared memory a chunk of 16 ahead (cp.async, two buffers)
+//   retention_scan        per (request, head, 32, 16 or 8 value columns): the recurrence over the portion's tokens,
+//                         one value column's state spread over the registers of 8, 16 or 32 lanes, the tokens'
+//                         q, k and v staged through shared memory a chunk of 16 ahead (cp.async, two buffers),
+//                         four tokens side by side
 //   retention_gated_norm  per (token, head): o / sqrt(mean(o^2) + eps) * silu(gate)
 //
 // A request's state row is [heads][vdim][dim] floats (a column of S is contiguous).  A portion that
-// starts at position 0 ignores what the row holds.  The read-out sums a column's dim products in a
-// fixed order, so results do not change with how a sequence is cut or batched.  Everything after the
-// projections is float.
+// starts at position 0 ignores what the row holds.  For a given number of lanes a column the read-out
+// sums a column's dim products in a fixed order with fixed roundings, so results do not change with
+// how a sequence is cut or batched; the launcher's `fixed_order` keeps that number at eight whatever
+// the step's shape (the 32-bit path), otherwise a lone prompt takes more lanes than a batch and the
+// two differ by rounding.  Everything after the projections is float.
 #include "common.cuh"
 
 #define RET_CHUNK 16             // tokens staged at a time
